@@ -32,6 +32,8 @@ class KVRequirement:
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None      # None: every earlier key; w: the last w keys
+    planes: int = 2                   # 2: keys and values apart; 1: one row per position (a latent that keys
+                                      # and values are both made from), and the view's v_pool is its k_pool
 
 
 @dataclass(frozen=True)
@@ -66,7 +68,9 @@ class _KVGroup:
         self.req = req
         self.entries = entries
         self.host = GroupTable(n_pages, page_size, max_slots, max_pages_per_seq, req.window)
-        self.storage = torch.zeros((len(entries), 2, n_pages, req.n_kv_heads, page_size, req.head_dim),
+        if req.planes not in (1, 2):
+            raise CacheError(f"a paged entry holds 1 or 2 rows per position, not {req.planes}")
+        self.storage = torch.zeros((len(entries), req.planes, n_pages, req.n_kv_heads, page_size, req.head_dim),
                                    dtype=dtype, device=device)
         self.table = torch.full((max_slots, max_pages_per_seq), -1, dtype=torch.int32, device=device)
 
@@ -192,7 +196,7 @@ class PagedCache:
         if entry not in self._kv_of_entry:
             return None
         g, i = self._kv_of_entry[entry]
-        return KVView(g.storage[i, 0], g.storage[i, 1], g.table, self.page_size, g.req.window)
+        return KVView(g.storage[i, 0], g.storage[i, g.req.planes - 1], g.table, self.page_size, g.req.window)
 
     def state_view(self, entry: int) -> Optional[torch.Tensor]:
         return self._state_of_entry.get(entry)
@@ -209,5 +213,5 @@ class PagedCache:
                              "the rotary table, 4 query position beyond the block table")
 
     def bytes_per_token(self) -> int:
-        return sum(2 * len(g.entries) * g.req.n_kv_heads * g.req.head_dim * g.storage.element_size()
+        return sum(g.req.planes * len(g.entries) * g.req.n_kv_heads * g.req.head_dim * g.storage.element_size()
                    for g in self.groups)

@@ -1,10 +1,13 @@
 from .base import (ConfigError, LayerSpec, ModelPlan, PartSpec, ScheduleEntry)
+from .fivitar import ARCHITECTURE as FIVITAR_ARCHITECTURE
+from .fivitar import FivitarConfig
 from .qwen3 import ARCHITECTURE as QWEN3_ARCHITECTURE
 from .qwen3 import Qwen3Config
-from .registry import (config_class_for, known_architectures, load_config,
+from .registry import (architecture_name, config_class_for, known_architectures, load_config,
                        register_architecture)
 
 register_architecture(QWEN3_ARCHITECTURE, Qwen3Config)
+register_architecture(FIVITAR_ARCHITECTURE, FivitarConfig)
 
-__all__ = ["ConfigError", "LayerSpec", "ModelPlan", "PartSpec", "ScheduleEntry", "Qwen3Config",
-           "config_class_for", "known_architectures", "load_config", "register_architecture"]
+__all__ = ["ConfigError", "LayerSpec", "ModelPlan", "PartSpec", "ScheduleEntry", "Qwen3Config", "FivitarConfig",
+           "architecture_name", "config_class_for", "known_architectures", "load_config", "register_architecture"]

@@ -35,9 +35,10 @@ class LayerSpec:
     """A block: which arrangement, and the parts it arranges."""
     block: str                      # registered block arrangement, e.g. "pre_norm_residual"
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]   # None: the layer has no feed-forward (the arrangement must allow that)
     norms: dict[str, PartSpec]      # arrangement-specific names, e.g. {"input": ..., "post_mixer": ...}
     position: Optional[str] = None  # key into ModelPlan.positions, None = the mixer takes no positions
+    gates: dict[str, PartSpec] = field(default_factory=dict)   # arrangement-specific gates on the sublayers' results
 
 
 @dataclass(frozen=True)

@@ -1,7 +1,8 @@
 """The one registry from an architecture's name to its model.
 
-config.json's `architectures[0]` picks the entry by exact match; an unknown
-name is an error that lists the known ones.  Upstream matches by substring in
+config.json's `architectures[0]` (or, in folders that name one model class as
+a string, `architecture`) picks the entry by exact match; an unknown name is
+an error that lists the known ones.  Upstream matches by substring in
 an if-chain and falls off the end of the function for an unknown name
 (src/models/model.cpp:10-34).
 
@@ -49,7 +50,15 @@ def load_config(model_dir):
         cfg = json.loads(path.read_text())
     except json.JSONDecodeError as e:
         raise ConfigError(f"{path}: not valid JSON: {e}") from None
+    return config_class_for(architecture_name(cfg, str(path))).from_dict(cfg, str(path))
+
+
+def architecture_name(cfg: dict, where: str = "config.json") -> str:
+    """The model class a config.json names: `architectures[0]`, or the string `architecture`."""
     archs = cfg.get("architectures")
+    if archs is None and isinstance(cfg.get("architecture"), str):
+        return cfg["architecture"]
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError(f"{path}: key 'architectures' must be a non-empty list of names")
-    return config_class_for(archs[0]).from_dict(cfg, str(path))
+        raise ConfigError(f"{where}: key 'architectures' must be a non-empty list of names "
+                          "(or 'architecture' one name)")
+    return archs[0]

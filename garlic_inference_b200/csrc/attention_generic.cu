@@ -12,6 +12,9 @@
 //
 //   o = softmax_j( q . k_j * scale ) v_j   over keys j <= pos, and j > pos - window
 //                                           when window > 0
+// With `sinks` (one number per query head) the softmax's denominator also holds exp(sink_h): a key without a
+// value, not scaled, counted once.  With d_v < d only the first d_v columns of a value row are summed and the
+// output rows are d_v wide (a cache whose rows serve as keys in full and as values in part).
 // Query head h reads key/value head h / (n_q / n_kv).  Scores, softmax and the
 // weighted sum are float32.  Upstream hands this to a library
 // (src/src-cuda/attention/fattn.cu:74-86: scale 1/sqrt(head_dim), causal mask
@@ -45,7 +48,7 @@ attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const
                     const int* __restrict__ block_table, const int* __restrict__ tok_pos,
                     const int* __restrict__ tok_slot, T* __restrict__ out, int n_q, int n_kv, int d,
                     int page_size, int max_pages, int n_pool_pages, int window, float scale,
-                    int* __restrict__ status) {
+                    const void* __restrict__ sinks, int sink_dtype, int d_v, int* __restrict__ status) {
     gi_pdl_start();
     extern __shared__ float smem[];
     float* q_s = smem;                       // d
@@ -55,11 +58,11 @@ attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const
 
     const int t = blockIdx.x, h = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    T* o = out + ((size_t)t * n_q + h) * d;
+    T* o = out + ((size_t)t * n_q + h) * d_v;
     const int slot = tok_slot[t];
     const int pos = tok_pos[t];
     if (slot < 0 || pos < 0 || pos / page_size >= max_pages) {
-        for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_f32<T>(0.f);
+        for (int i = threadIdx.x; i < d_v; i += blockDim.x) o[i] = from_f32<T>(0.f);
         if (slot >= 0 && threadIdx.x == 0) atomicExch(status, 4);
         return;
     }
@@ -111,7 +114,7 @@ attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const
 #pragma unroll
             for (int r = 0; r < DPL; ++r) {
                 const int i = lane + 32 * r;
-                if (i < d) acc[r] += pj * to_f32(vr[i]);
+                if (i < d_v) acc[r] += pj * to_f32(vr[i]);
             }
         }
     }
@@ -124,9 +127,12 @@ attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const
     __syncthreads();
     float M = -INFINITY;
     for (int w = 0; w < AG_WARPS; ++w) M = fmaxf(M, m_s[w]);
+    const float sink = sinks ? load_w(sinks, sink_dtype, h) : -INFINITY;
+    M = fmaxf(M, sink);
     float L = 0.f;
     for (int w = 0; w < AG_WARPS; ++w) L += (m_s[w] == -INFINITY ? 0.f : expf(m_s[w] - M) * l_s[w]);
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    if (sinks) L += expf(sink - M);
+    for (int i = threadIdx.x; i < d_v; i += blockDim.x) {
         float v = 0.f;
         for (int w = 0; w < AG_WARPS; ++w)
             if (m_s[w] != -INFINITY) v += expf(m_s[w] - M) * acc_s[w * d + i];
@@ -138,13 +144,13 @@ template <typename T>
 static int launch_generic(const void* q, const void* k_pool, const void* v_pool, const int* block_table,
                           const int* tok_pos, const int* tok_slot, void* out, int n_tokens, int n_q, int n_kv,
                           int d, int page_size, int max_pages, int n_pool_pages, int window, float scale,
-                          int* status, cudaStream_t s) {
+                          const void* sinks, int sink_dtype, int d_v, int* status, cudaStream_t s) {
     dim3 grid(n_tokens, n_q);
     const size_t smem = ((size_t)d * (1 + AG_WARPS) + 2 * AG_WARPS) * sizeof(float);
 #define AG_LAUNCH(DPL)                                                                               \
     gi_launch(attn_generic_kernel<T, DPL>, grid, dim3(AG_WARPS * 32), smem, s,                                     \
         (const T*)q, (const T*)k_pool, (const T*)v_pool, block_table, tok_pos, tok_slot, (T*)out,     \
-        n_q, n_kv, d, page_size, max_pages, n_pool_pages, window, scale, status)
+        n_q, n_kv, d, page_size, max_pages, n_pool_pages, window, scale, sinks, sink_dtype, d_v, status)
     if (d <= 32) AG_LAUNCH(1);
     else if (d <= 64) AG_LAUNCH(2);
     else if (d <= 128) AG_LAUNCH(4);
@@ -157,20 +163,21 @@ static int launch_generic(const void* q, const void* k_pool, const void* v_pool,
 extern "C" int gi_attention_generic(const void* q, const void* k_pool, const void* v_pool, int act_dtype,
                                     const int* block_table, const int* tok_pos, const int* tok_slot,
                                     void* out, int n_tokens, int n_q, int n_kv, int d, int page_size,
-                                    int max_pages, int n_pool_pages, int window, float scale, int* status,
-                                    void* stream) {
+                                    int max_pages, int n_pool_pages, int window, float scale, const void* sinks,
+                                    int sink_dtype, int d_v, int* status, void* stream) {
     GI_REQUIRE(n_tokens >= 0 && n_q > 0 && n_kv > 0 && d > 0, "gi_attention_generic: sizes must be positive");
     GI_REQUIRE(n_q % n_kv == 0, "gi_attention_generic: %d query heads are no multiple of %d key/value heads", n_q, n_kv);
     GI_REQUIRE(d % 8 == 0 && d <= 512, "gi_attention_generic: head_dim %d must be a multiple of 8, at most 512", d);
     GI_REQUIRE(n_q <= 65535, "gi_attention_generic: %d query heads is beyond 65535", n_q);
+    GI_REQUIRE(d_v > 0 && d_v <= d, "gi_attention_generic: %d value columns of rows of %d", d_v, d);
     GI_REQUIRE(page_size > 0 && max_pages > 0 && window >= 0, "gi_attention_generic: page size, table width and window");
     if (n_tokens == 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     if (act_dtype == GI_DTYPE_F32)
         return launch_generic<float>(q, k_pool, v_pool, block_table, tok_pos, tok_slot, out, n_tokens, n_q, n_kv, d,
-                                     page_size, max_pages, n_pool_pages, window, scale, status, s);
+                                     page_size, max_pages, n_pool_pages, window, scale, sinks, sink_dtype, d_v, status, s);
     if (act_dtype == GI_DTYPE_BF16)
         return launch_generic<bf16>(q, k_pool, v_pool, block_table, tok_pos, tok_slot, out, n_tokens, n_q, n_kv, d,
-                                    page_size, max_pages, n_pool_pages, window, scale, status, s);
+                                    page_size, max_pages, n_pool_pages, window, scale, sinks, sink_dtype, d_v, status, s);
     GI_REQUIRE(false, "gi_attention_generic: activation dtype %d", act_dtype);
 }

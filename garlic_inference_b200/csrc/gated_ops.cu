@@ -1,0 +1,148 @@
+// Row-wise kernels of layers whose sublayer results are gated and normed before they join the residual
+// stream, and of mixers whose read-out is normed per group and gated.
+//
+//   gi_gate_norm_add        x += rmsnorm( y * sigmoid(g + b) ) * w     (x the float32 residual stream; the gate is
+//                           optional), with a copy of the new x in the activation type for the next products
+//   gi_xielu                a(z) = softplus(p) z^2 + z/2                         z > 0
+//                                  (1/2 + softplus(q)) (e^z - 1 - z) + z/2       z <= 0
+//   gi_gated_group_rmsnorm  out = o / rms(o over its group) * w * gate(g),  gate = sigmoid or silu
+//
+// Everything is float32 inside and rounded once on the way out; T is the activation type.  Block sizes depend
+// on the row's width alone, so a row's result does not depend on what else is in the launch.
+// NikolayBlagoev/garlic-inference has none of these (its one layer is pre-norm with a plain residual add,
+// src/src-cuda/norm.cu:51-101).
+#include "common.cuh"
+#include <math.h>
+
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+// ------------------------------------------------------------------ gate, norm, add
+template <typename T>
+__global__ void gate_norm_add_kernel(const T* __restrict__ y, long long ldy, const T* __restrict__ g, long long ldg,
+                                     const void* __restrict__ bias, int b_dtype, const void* __restrict__ weight,
+                                     int w_dtype, float* __restrict__ residual, T* __restrict__ act_out, int dim,
+                                     float eps) {
+    gi_pdl_start();
+    extern __shared__ float row[];               // dim gated values, then 33 for the reduction
+    float* red = row + dim;
+    const size_t r = blockIdx.x;
+    const T* yr = y + r * ldy;
+    const T* gr = g ? g + r * ldg : nullptr;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+        float s = to_f32(yr[c]);
+        if (gr) s *= sigmoid_f(to_f32(gr[c]) + (bias ? load_w(bias, b_dtype, c) : 0.f));
+        row[c] = s;
+        ss += s * s;
+    }
+    ss = block_sum(ss, red);
+    const float inv = 1.f / sqrtf(ss / (float)dim + eps);
+    float* res = residual + r * dim;
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+        const float x = res[c] + row[c] * inv * load_w(weight, w_dtype, c);
+        res[c] = x;
+        if (act_out) act_out[r * dim + c] = from_f32<T>(x);
+    }
+}
+
+extern "C" int gi_gate_norm_add(const void* y, long long ldy, const void* g, long long ldg, const void* bias,
+                                int b_dtype, const void* weight, int w_dtype, float* residual, void* act_out,
+                                int act_dtype, int n_rows, int dim, float eps, void* stream) {
+    GI_REQUIRE(n_rows >= 0 && dim > 0 && dim <= 16384, "gi_gate_norm_add: rows of %d elements (at most 16384)", dim);
+    GI_REQUIRE(ldy >= dim && (!g || ldg >= dim), "gi_gate_norm_add: row strides shorter than the rows");
+    if (n_rows == 0) return 0;
+    const int threads = dim >= 1024 ? 256 : 128;
+    const size_t smem = ((size_t)dim + 33) * sizeof(float);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (act_dtype == GI_DTYPE_F32) {
+        if (smem > 48 * 1024) { int rc = gi_reserve_smem((const void*)gate_norm_add_kernel<float>, smem, "gi_gate_norm_add"); if (rc) return rc; }
+        gi_launch(gate_norm_add_kernel<float>, dim3(n_rows), dim3(threads), smem, s, (const float*)y, ldy, (const float*)g,
+                  ldg, bias, b_dtype, weight, w_dtype, residual, (float*)act_out, dim, eps);
+    } else if (act_dtype == GI_DTYPE_BF16) {
+        if (smem > 48 * 1024) { int rc = gi_reserve_smem((const void*)gate_norm_add_kernel<bf16>, smem, "gi_gate_norm_add"); if (rc) return rc; }
+        gi_launch(gate_norm_add_kernel<bf16>, dim3(n_rows), dim3(threads), smem, s, (const bf16*)y, ldy, (const bf16*)g,
+                  ldg, bias, b_dtype, weight, w_dtype, residual, (bf16*)act_out, dim, eps);
+    } else {
+        GI_REQUIRE(false, "gi_gate_norm_add: activation dtype %d", act_dtype);
+    }
+    return gi_check_launch("gi_gate_norm_add");
+}
+
+// ------------------------------------------------------------------ xIELU
+template <typename T>
+__global__ void xielu_kernel(const T* __restrict__ z, long long ldz, T* __restrict__ out, const void* __restrict__ pq,
+                             int pq_dtype, int n_rows, int cols) {
+    gi_pdl_start();
+    const float a_pos = softplus_f(load_w(pq, pq_dtype, 0));
+    const float a_neg = 0.5f + softplus_f(load_w(pq, pq_dtype, 1));
+    const long long total = (long long)n_rows * cols;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / cols;
+        const int c = (int)(i - r * cols);
+        const float v = to_f32(z[r * ldz + c]);
+        const float a = v > 0.f ? a_pos * v * v + 0.5f * v : a_neg * (expm1f(v) - v) + 0.5f * v;
+        out[i] = from_f32<T>(a);
+    }
+}
+
+extern "C" int gi_xielu(const void* z, long long ldz, void* out, int act_dtype, const void* pq, int pq_dtype,
+                        int n_rows, int cols, void* stream) {
+    GI_REQUIRE(n_rows >= 0 && cols > 0 && ldz >= cols, "gi_xielu: sizes");
+    if (n_rows == 0) return 0;
+    const long long total = (long long)n_rows * cols;
+    const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (act_dtype == GI_DTYPE_F32)
+        gi_launch(xielu_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)z, ldz, (float*)out, pq, pq_dtype, n_rows, cols);
+    else if (act_dtype == GI_DTYPE_BF16)
+        gi_launch(xielu_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (const bf16*)z, ldz, (bf16*)out, pq, pq_dtype, n_rows, cols);
+    else
+        GI_REQUIRE(false, "gi_xielu: activation dtype %d", act_dtype);
+    return gi_check_launch("gi_xielu");
+}
+
+// ------------------------------------------------------------------ group norm and gate of a read-out
+// o float32 [n, groups * gs]; one block per (row, group).  weight[c % w_len]: w_len = gs (one weight for all
+// groups) or groups * gs.  gate_kind 0: sigmoid(g), 1: silu(g); g has the columns of o, row stride ldg.
+template <typename T>
+__global__ void gated_group_rmsnorm_kernel(const float* __restrict__ o, const T* __restrict__ g, long long ldg,
+                                           const void* __restrict__ weight, int w_dtype, int w_len,
+                                           T* __restrict__ out, int groups, int gs, float eps, int gate_kind) {
+    gi_pdl_start();
+    __shared__ float red[33];
+    const size_t r = blockIdx.x;
+    const int grp = blockIdx.y;
+    const float* orow = o + (r * groups + grp) * gs;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < gs; c += blockDim.x) ss += orow[c] * orow[c];
+    ss = block_sum(ss, red);
+    const float inv = 1.f / sqrtf(ss / (float)gs + eps);
+    for (int c = threadIdx.x; c < gs; c += blockDim.x) {
+        const int col = grp * gs + c;
+        const float z = to_f32(g[r * ldg + col]);
+        const float gate = gate_kind == 0 ? sigmoid_f(z) : z * sigmoid_f(z);
+        out[r * (size_t)groups * gs + col] = from_f32<T>(orow[c] * inv * load_w(weight, w_dtype, col % w_len) * gate);
+    }
+}
+
+extern "C" int gi_gated_group_rmsnorm(const float* o, const void* g, long long ldg, const void* weight, int w_dtype,
+                                      int w_len, void* out, int act_dtype, int n_rows, int groups, int gs, float eps,
+                                      int gate_kind, void* stream) {
+    GI_REQUIRE(n_rows >= 0 && groups > 0 && gs > 0 && groups <= 65535, "gi_gated_group_rmsnorm: sizes");
+    GI_REQUIRE(w_len == gs || w_len == groups * gs, "gi_gated_group_rmsnorm: a weight of %d elements fits neither a "
+               "group of %d nor the row of %d", w_len, gs, groups * gs);
+    GI_REQUIRE(ldg >= (long long)groups * gs && (gate_kind == 0 || gate_kind == 1), "gi_gated_group_rmsnorm: gate");
+    if (n_rows == 0) return 0;
+    const int threads = gs >= 1024 ? 256 : (gs >= 128 ? 128 : (gs > 32 ? 64 : 32));
+    cudaStream_t s = (cudaStream_t)stream;
+    if (act_dtype == GI_DTYPE_F32)
+        gi_launch(gated_group_rmsnorm_kernel<float>, dim3(n_rows, groups), dim3(threads), 0, s, o, (const float*)g, ldg,
+                  weight, w_dtype, w_len, (float*)out, groups, gs, eps, gate_kind);
+    else if (act_dtype == GI_DTYPE_BF16)
+        gi_launch(gated_group_rmsnorm_kernel<bf16>, dim3(n_rows, groups), dim3(threads), 0, s, o, (const bf16*)g, ldg,
+                  weight, w_dtype, w_len, (bf16*)out, groups, gs, eps, gate_kind);
+    else
+        GI_REQUIRE(false, "gi_gated_group_rmsnorm: activation dtype %d", act_dtype);
+    return gi_check_launch("gi_gated_group_rmsnorm");
+}

@@ -1,0 +1,367 @@
+// Mixers that carry a matrix of state per head from token to token, and the short causal convolution in
+// front of one of them.  All state is float32 and lives in the cache's per-slot state rows.
+//
+//   gi_causal_conv_silu     y[t, c] = silu( sum_j taps[c, j] x[t - (K-1) + j, c] ), zeros before position 0; the
+//                           K-1 inputs before this step's first token come from the slot's state
+//   gi_conv_state_update    afterwards: the slot's state becomes its last K-1 inputs
+//   gi_decay_scan           S_t = lam_h S_(t-1) + k_t v_t^T,  o_t = S_t^T q_t           (q, k, v = silu of the
+//                           projections): linear attention with one fixed decay per head
+//   gi_delta_scan           S <- g_t S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t
+//                           with q, k made unit vectors per head (q also times dim^-1/2),
+//                           g_t = exp(-exp(A_h) softplus(a_t + dt_h)),  beta_t = sigmoid(b_t): the gated delta rule
+//
+// A scan block owns one (sequence, head, slice of 32 value columns) and walks the sequence's tokens of this
+// step in order, so prompts, portions of prompts and single tokens run the same instructions in the same
+// order and give the same bits.  A thread holds, for one value column, a quarter of the key dimension in
+// registers (4 consecutive keys out of every 16); sums over the key dimension end with two shuffles.
+// State rows are laid out [head][value column][key, padded to 4 R] so that a warp's loads and stores are
+// whole 64-byte runs.  NikolayBlagoev/garlic-inference has no recurrent mixer.
+#include "common.cuh"
+#include <math.h>
+
+__device__ __forceinline__ float rc_sigmoid(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float rc_silu(float z) { return z / (1.f + expf(-z)); }
+__device__ __forceinline__ float rc_softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+// ------------------------------------------------------------------ short causal convolution
+#define CONV_MAX_TAPS 16
+
+// In-step predecessors of row r that belong to the same sequence, at most `most`.
+__device__ __forceinline__ int rows_before(const int* __restrict__ tok_slot, int r, int slot, int most) {
+    int have = 0;
+    while (have < most && r - have - 1 >= 0 && tok_slot[r - have - 1] == slot) ++have;
+    return have;
+}
+
+template <typename T>
+__global__ void causal_conv_silu_kernel(const T* __restrict__ x, long long ldx, int C, const void* __restrict__ taps,
+                                        int taps_dtype, int K, const float* __restrict__ state, long long state_stride,
+                                        const int* __restrict__ tok_slot, float* __restrict__ out) {
+    gi_pdl_start();
+    const int r = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int slot = tok_slot[r];
+    const int have = slot < 0 ? 0 : rows_before(tok_slot, r, slot, K - 1);
+    float acc = 0.f;
+    for (int j = K - 1; j >= 0; --j) {               // oldest input first, whatever its source
+        float xv = 0.f;
+        if (j <= have) xv = to_f32(x[(size_t)(r - j) * ldx + c]);
+        else if (slot >= 0) xv = state[(size_t)slot * state_stride + (size_t)(K - 1 + have - j) * C + c];
+        acc = fmaf(load_w(taps, taps_dtype, c * K + (K - 1 - j)), xv, acc);
+    }
+    out[(size_t)r * C + c] = rc_silu(acc);
+}
+
+template <typename T>
+__global__ void conv_state_update_kernel(const T* __restrict__ x, long long ldx, int C, int K,
+                                         float* __restrict__ state, long long state_stride,
+                                         const int* __restrict__ tok_slot, int n_rows) {
+    gi_pdl_start();
+    const int r = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int slot = tok_slot[r];
+    if (slot < 0 || (r + 1 < n_rows && tok_slot[r + 1] == slot)) return;      // only a sequence's last row acts
+    const int have = rows_before(tok_slot, r, slot, K - 1);
+    float* st = state + (size_t)slot * state_stride;
+    float vals[CONV_MAX_TAPS];
+    for (int m = 0; m < K - 1; ++m) {
+        const int j = K - 2 - m;                     // how far before the last row
+        vals[m] = j <= have ? to_f32(x[(size_t)(r - j) * ldx + c]) : st[(size_t)(K - 1 + have - j) * C + c];
+    }
+    for (int m = 0; m < K - 1; ++m) st[(size_t)m * C + c] = vals[m];
+}
+
+extern "C" int gi_causal_conv_silu(const void* x, long long ldx, int act_dtype, int C, const void* taps, int taps_dtype,
+                                   int K, float* state, long long state_stride, const int* tok_slot, float* out,
+                                   int n_rows, int update_state, void* stream) {
+    GI_REQUIRE(n_rows >= 0 && C > 0 && K >= 1 && K <= CONV_MAX_TAPS, "gi_causal_conv_silu: %d channels, %d taps (1 to %d)",
+               C, K, CONV_MAX_TAPS);
+    GI_REQUIRE(ldx >= C && state_stride >= (long long)(K - 1) * C, "gi_causal_conv_silu: strides shorter than the rows");
+    GI_REQUIRE(n_rows <= 65535, "gi_causal_conv_silu: %d rows in one step is beyond 65535", n_rows);
+    if (n_rows == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid((C + 127) / 128, n_rows);
+    if (act_dtype == GI_DTYPE_F32) {
+        if (!update_state) gi_launch(causal_conv_silu_kernel<float>, grid, dim3(128), 0, s, (const float*)x, ldx, C, taps, taps_dtype, K, (const float*)state, state_stride, tok_slot, out);
+        else if (K > 1) gi_launch(conv_state_update_kernel<float>, grid, dim3(128), 0, s, (const float*)x, ldx, C, K, state, state_stride, tok_slot, n_rows);
+    } else if (act_dtype == GI_DTYPE_BF16) {
+        if (!update_state) gi_launch(causal_conv_silu_kernel<bf16>, grid, dim3(128), 0, s, (const bf16*)x, ldx, C, taps, taps_dtype, K, (const float*)state, state_stride, tok_slot, out);
+        else if (K > 1) gi_launch(conv_state_update_kernel<bf16>, grid, dim3(128), 0, s, (const bf16*)x, ldx, C, K, state, state_stride, tok_slot, n_rows);
+    } else {
+        GI_REQUIRE(false, "gi_causal_conv_silu: activation dtype %d", act_dtype);
+    }
+    return gi_check_launch("gi_causal_conv_silu");
+}
+
+// ------------------------------------------------------------------ scans
+#define SCAN_TC 8            // tokens staged in shared memory at a time
+#define SCAN_VS 32           // value columns per block
+#define SCAN_THREADS 128
+
+// Where a sequence's rows are: from `spans` [n_seq, 3] = {slot, first row, rows}, or, without spans, sequence
+// i is row i alone (a decode step: the slot comes from tok_slot).
+__device__ __forceinline__ void scan_span(const int* __restrict__ spans, const int* __restrict__ tok_slot, int seq,
+                                          int& slot, int& start, int& len) {
+    if (spans) { slot = spans[3 * seq]; start = spans[3 * seq + 1]; len = spans[3 * seq + 2]; }
+    else { slot = tok_slot[seq]; start = seq; len = 1; }
+}
+
+// A thread's R state values: register e = 4 i + w holds key (4 i + part) * 4 + w of its value column.
+#define KEY_OF(i, part) (((i) * 4 + (part)) * 4)
+
+template <int R>
+__device__ __forceinline__ void scan_load_state(float (&S)[R], const float* __restrict__ st, int part) {
+#pragma unroll
+    for (int i = 0; i < R / 4; ++i) {
+        const float4 v = *reinterpret_cast<const float4*>(st + KEY_OF(i, part));
+        S[4 * i] = v.x; S[4 * i + 1] = v.y; S[4 * i + 2] = v.z; S[4 * i + 3] = v.w;
+    }
+}
+template <int R>
+__device__ __forceinline__ void scan_store_state(const float (&S)[R], float* __restrict__ st, int part) {
+#pragma unroll
+    for (int i = 0; i < R / 4; ++i)
+        *reinterpret_cast<float4*>(st + KEY_OF(i, part)) = make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]);
+}
+__device__ __forceinline__ float quad_sum(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    return v;
+}
+
+// ---- linear attention with a fixed decay per head
+// qkv: T [n, ld], silu applied here; q at column q_off + h d, k at k_off + h d, v at v_off + h dv.
+template <typename T, int R>
+__global__ void __launch_bounds__(SCAN_THREADS)
+decay_scan_kernel(const T* __restrict__ qkv, long long ld, int q_off, int k_off, int v_off,
+                  const float* __restrict__ decay, float* __restrict__ state, long long state_stride,
+                  const int* __restrict__ spans, const int* __restrict__ tok_slot, float* __restrict__ out,
+                  int H, int d, int dv) {
+    gi_pdl_start();
+    constexpr int DP = 4 * R;                          // padded key dimension
+    __shared__ __align__(16) float q_s[SCAN_TC][DP];
+    __shared__ __align__(16) float k_s[SCAN_TC][DP];
+    __shared__ float v_s[SCAN_TC][SCAN_VS];
+    __shared__ float o_s[SCAN_TC][SCAN_VS];
+    int slot, start, len;
+    scan_span(spans, tok_slot, blockIdx.x, slot, start, len);
+    const int h = blockIdx.y, v0 = blockIdx.z * SCAN_VS;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int part = lane & 3, vl = warp * 8 + (lane >> 2), v = v0 + vl;
+    const bool live = v < dv;
+    if (slot < 0) {
+        for (int t = 0; t < len; ++t)
+            if (live && part == 0) out[(size_t)(start + t) * H * dv + h * dv + v] = 0.f;
+        return;
+    }
+    const float lam = decay[h];
+    float* st = state + (size_t)slot * state_stride + ((size_t)h * dv + (live ? v : 0)) * DP;
+    float S[R];
+    if (live) scan_load_state<R>(S, st, part);
+    else {
+#pragma unroll
+        for (int e = 0; e < R; ++e) S[e] = 0.f;
+    }
+    for (int t0 = 0; t0 < len; t0 += SCAN_TC) {
+        const int tc = min(SCAN_TC, len - t0);
+        __syncthreads();                               // the last chunk's o_s and inputs are done with
+        for (int i = threadIdx.x; i < tc * DP; i += SCAN_THREADS) {
+            const int t = i / DP, c = i - t * DP;
+            const T* row = qkv + (size_t)(start + t0 + t) * ld;
+            q_s[t][c] = c < d ? rc_silu(to_f32(row[q_off + h * d + c])) : 0.f;
+            k_s[t][c] = c < d ? rc_silu(to_f32(row[k_off + h * d + c])) : 0.f;
+        }
+        for (int i = threadIdx.x; i < tc * SCAN_VS; i += SCAN_THREADS) {
+            const int t = i / SCAN_VS, c = i - t * SCAN_VS;
+            v_s[t][c] = v0 + c < dv ? rc_silu(to_f32(qkv[(size_t)(start + t0 + t) * ld + v_off + h * dv + v0 + c])) : 0.f;
+        }
+        __syncthreads();
+        for (int t = 0; t < tc; ++t) {
+            const float vt = v_s[t][vl];
+            float o = 0.f;
+#pragma unroll
+            for (int i = 0; i < R / 4; ++i) {
+                const float4 kk = *reinterpret_cast<const float4*>(&k_s[t][KEY_OF(i, part)]);
+                const float4 qq = *reinterpret_cast<const float4*>(&q_s[t][KEY_OF(i, part)]);
+                S[4 * i] = fmaf(lam, S[4 * i], kk.x * vt);          o = fmaf(S[4 * i], qq.x, o);
+                S[4 * i + 1] = fmaf(lam, S[4 * i + 1], kk.y * vt);  o = fmaf(S[4 * i + 1], qq.y, o);
+                S[4 * i + 2] = fmaf(lam, S[4 * i + 2], kk.z * vt);  o = fmaf(S[4 * i + 2], qq.z, o);
+                S[4 * i + 3] = fmaf(lam, S[4 * i + 3], kk.w * vt);  o = fmaf(S[4 * i + 3], qq.w, o);
+            }
+            o = quad_sum(o);
+            if (part == 0) o_s[t][vl] = o;
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < tc * SCAN_VS; i += SCAN_THREADS) {
+            const int t = i / SCAN_VS, c = i - t * SCAN_VS;
+            if (v0 + c < dv) out[(size_t)(start + t0 + t) * H * dv + h * dv + v0 + c] = o_s[t][c];
+        }
+    }
+    if (live) scan_store_state<R>(S, st, part);
+}
+
+// ---- the gated delta rule
+// qkv: float32 [n, ldq] (the convolution's output): q of key head kh at q_off + kh d, k at k_off + kh d, v of
+// head h at v_off + h dv.  ab: T [n, ldab]: beta's logit of head h at column b_off + h, the decay's at a_off + h.
+template <typename T, int R>
+__global__ void __launch_bounds__(SCAN_THREADS)
+delta_scan_kernel(const float* __restrict__ qkv, long long ldq, int q_off, int k_off, int v_off,
+                  const T* __restrict__ ab, long long ldab, int b_off, int a_off,
+                  const void* __restrict__ A_log, const void* __restrict__ dt_bias, int p_dtype,
+                  float* __restrict__ state, long long state_stride, const int* __restrict__ spans,
+                  const int* __restrict__ tok_slot, float* __restrict__ out, int H, int Hk, int d, int dv,
+                  float unit_eps, float q_scale) {
+    gi_pdl_start();
+    constexpr int DP = 4 * R;
+    __shared__ __align__(16) float q_s[SCAN_TC][DP];
+    __shared__ __align__(16) float k_s[SCAN_TC][DP];
+    __shared__ float v_s[SCAN_TC][SCAN_VS];
+    __shared__ float o_s[SCAN_TC][SCAN_VS];
+    __shared__ float g_s[SCAN_TC], b_s[SCAN_TC];
+    int slot, start, len;
+    scan_span(spans, tok_slot, blockIdx.x, slot, start, len);
+    const int h = blockIdx.y, v0 = blockIdx.z * SCAN_VS;
+    const int kh = h / (H / Hk);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int part = lane & 3, vl = warp * 8 + (lane >> 2), v = v0 + vl;
+    const bool live = v < dv;
+    if (slot < 0) {
+        for (int t = 0; t < len; ++t)
+            if (live && part == 0) out[(size_t)(start + t) * H * dv + h * dv + v] = 0.f;
+        return;
+    }
+    const float rate = expf(load_w(A_log, p_dtype, h)), dt = load_w(dt_bias, p_dtype, h);
+    float* st = state + (size_t)slot * state_stride + ((size_t)h * dv + (live ? v : 0)) * DP;
+    float S[R];
+    if (live) scan_load_state<R>(S, st, part);
+    else {
+#pragma unroll
+        for (int e = 0; e < R; ++e) S[e] = 0.f;
+    }
+    for (int t0 = 0; t0 < len; t0 += SCAN_TC) {
+        const int tc = min(SCAN_TC, len - t0);
+        __syncthreads();
+        // each warp stages tokens warp, warp + 4: q and k as unit vectors (sum of squares in lane order, then a tree)
+        for (int t = warp; t < tc; t += SCAN_THREADS / 32) {
+            const float* row = qkv + (size_t)(start + t0 + t) * ldq;
+            float sq = 0.f, sk = 0.f;
+            for (int c = lane; c < DP; c += 32) {
+                const float qv = c < d ? row[q_off + kh * d + c] : 0.f;
+                const float kv = c < d ? row[k_off + kh * d + c] : 0.f;
+                q_s[t][c] = qv; k_s[t][c] = kv;
+                sq = fmaf(qv, qv, sq); sk = fmaf(kv, kv, sk);
+            }
+            sq = warp_sum(sq); sk = warp_sum(sk);
+            const float iq = q_scale / sqrtf(sq + unit_eps), ik = 1.f / sqrtf(sk + unit_eps);
+            for (int c = lane; c < DP; c += 32) { q_s[t][c] *= iq; k_s[t][c] *= ik; }
+            if (lane == 0) {
+                const T* abr = ab + (size_t)(start + t0 + t) * ldab;
+                g_s[t] = expf(-rate * rc_softplus(to_f32(abr[a_off + h]) + dt));
+                b_s[t] = rc_sigmoid(to_f32(abr[b_off + h]));
+            }
+            v_s[t][lane] = v0 + lane < dv ? row[v_off + h * dv + v0 + lane] : 0.f;
+        }
+        __syncthreads();
+        for (int t = 0; t < tc; ++t) {
+            const float g = g_s[t];
+            float r = 0.f;
+#pragma unroll
+            for (int i = 0; i < R / 4; ++i) {
+                const float4 kk = *reinterpret_cast<const float4*>(&k_s[t][KEY_OF(i, part)]);
+                S[4 * i] *= g;      r = fmaf(S[4 * i], kk.x, r);
+                S[4 * i + 1] *= g;  r = fmaf(S[4 * i + 1], kk.y, r);
+                S[4 * i + 2] *= g;  r = fmaf(S[4 * i + 2], kk.z, r);
+                S[4 * i + 3] *= g;  r = fmaf(S[4 * i + 3], kk.w, r);
+            }
+            r = quad_sum(r);
+            const float u = b_s[t] * (v_s[t][vl] - r);
+            float o = 0.f;
+#pragma unroll
+            for (int i = 0; i < R / 4; ++i) {
+                const float4 kk = *reinterpret_cast<const float4*>(&k_s[t][KEY_OF(i, part)]);
+                const float4 qq = *reinterpret_cast<const float4*>(&q_s[t][KEY_OF(i, part)]);
+                S[4 * i] = fmaf(kk.x, u, S[4 * i]);          o = fmaf(S[4 * i], qq.x, o);
+                S[4 * i + 1] = fmaf(kk.y, u, S[4 * i + 1]);  o = fmaf(S[4 * i + 1], qq.y, o);
+                S[4 * i + 2] = fmaf(kk.z, u, S[4 * i + 2]);  o = fmaf(S[4 * i + 2], qq.z, o);
+                S[4 * i + 3] = fmaf(kk.w, u, S[4 * i + 3]);  o = fmaf(S[4 * i + 3], qq.w, o);
+            }
+            o = quad_sum(o);
+            if (part == 0) o_s[t][vl] = o;
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < tc * SCAN_VS; i += SCAN_THREADS) {
+            const int t = i / SCAN_VS, c = i - t * SCAN_VS;
+            if (v0 + c < dv) out[(size_t)(start + t0 + t) * H * dv + h * dv + v0 + c] = o_s[t][c];
+        }
+    }
+    if (live) scan_store_state<R>(S, st, part);
+}
+
+// Registers per thread for a key dimension: the smallest of 4, 8, 16, 32, 64 with 4 R >= d (0: too large).
+static int scan_regs(int d) {
+    for (int r = 4; r <= 64; r *= 2)
+        if (4 * r >= d) return r;
+    return 0;
+}
+
+// Floats of one head's state for key dimension d and value dimension dv, as the scans lay it out.
+extern "C" long long gi_scan_state_floats(int d, int dv) {
+    const int r = scan_regs(d);
+    return r ? (long long)dv * 4 * r : -1;
+}
+
+#define SCAN_DISPATCH(KERNEL, TT, ...)                                                         \
+    switch (R) {                                                                               \
+        case 4:  gi_launch(KERNEL<TT, 4>, grid, dim3(SCAN_THREADS), 0, s, __VA_ARGS__); break;  \
+        case 8:  gi_launch(KERNEL<TT, 8>, grid, dim3(SCAN_THREADS), 0, s, __VA_ARGS__); break;  \
+        case 16: gi_launch(KERNEL<TT, 16>, grid, dim3(SCAN_THREADS), 0, s, __VA_ARGS__); break; \
+        case 32: gi_launch(KERNEL<TT, 32>, grid, dim3(SCAN_THREADS), 0, s, __VA_ARGS__); break; \
+        default: gi_launch(KERNEL<TT, 64>, grid, dim3(SCAN_THREADS), 0, s, __VA_ARGS__); break; \
+    }
+
+extern "C" int gi_decay_scan(const void* qkv, long long ld, int act_dtype, int q_off, int k_off, int v_off,
+                             const float* decay, float* state, long long state_stride, const int* spans,
+                             const int* tok_slot, float* out, int n_seq, int H, int d, int dv, void* stream) {
+    const int R = scan_regs(d);
+    GI_REQUIRE(n_seq >= 0 && H > 0 && d > 0 && dv > 0 && R > 0, "gi_decay_scan: key dimension %d (at most 256)", d);
+    GI_REQUIRE(H <= 65535 && (dv + SCAN_VS - 1) / SCAN_VS <= 65535, "gi_decay_scan: %d heads of %d values", H, dv);
+    GI_REQUIRE(state_stride >= (long long)H * dv * 4 * R && state_stride % 4 == 0, "gi_decay_scan: state rows of %lld "
+               "floats are shorter than %lld or no multiple of 4", state_stride, (long long)H * dv * 4 * R);
+    if (n_seq == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid(n_seq, H, (dv + SCAN_VS - 1) / SCAN_VS);
+    if (act_dtype == GI_DTYPE_F32) {
+        SCAN_DISPATCH(decay_scan_kernel, float, (const float*)qkv, ld, q_off, k_off, v_off, decay, state, state_stride, spans, tok_slot, out, H, d, dv)
+    } else if (act_dtype == GI_DTYPE_BF16) {
+        SCAN_DISPATCH(decay_scan_kernel, bf16, (const bf16*)qkv, ld, q_off, k_off, v_off, decay, state, state_stride, spans, tok_slot, out, H, d, dv)
+    } else {
+        GI_REQUIRE(false, "gi_decay_scan: activation dtype %d", act_dtype);
+    }
+    return gi_check_launch("gi_decay_scan");
+}
+
+extern "C" int gi_delta_scan(const float* qkv, long long ldq, int q_off, int k_off, int v_off, const void* ab,
+                             long long ldab, int act_dtype, int b_off, int a_off, const void* A_log, const void* dt_bias,
+                             int p_dtype, float* state, long long state_stride, const int* spans, const int* tok_slot,
+                             float* out, int n_seq, int H, int Hk, int d, int dv, float unit_eps, float q_scale,
+                             void* stream) {
+    const int R = scan_regs(d);
+    GI_REQUIRE(n_seq >= 0 && H > 0 && Hk > 0 && H % Hk == 0 && d > 0 && dv > 0 && R > 0,
+               "gi_delta_scan: %d heads on %d key heads, key dimension %d (at most 256)", H, Hk, d);
+    GI_REQUIRE(H <= 65535 && (dv + SCAN_VS - 1) / SCAN_VS <= 65535, "gi_delta_scan: %d heads of %d values", H, dv);
+    GI_REQUIRE(state_stride >= (long long)H * dv * 4 * R && state_stride % 4 == 0, "gi_delta_scan: state rows of %lld "
+               "floats are shorter than %lld or no multiple of 4", state_stride, (long long)H * dv * 4 * R);
+    if (n_seq == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid(n_seq, H, (dv + SCAN_VS - 1) / SCAN_VS);
+    if (act_dtype == GI_DTYPE_F32) {
+        SCAN_DISPATCH(delta_scan_kernel, float, qkv, ldq, q_off, k_off, v_off, (const float*)ab, ldab, b_off, a_off, A_log, dt_bias, p_dtype, state, state_stride, spans, tok_slot, out, H, Hk, d, dv, unit_eps, q_scale)
+    } else if (act_dtype == GI_DTYPE_BF16) {
+        SCAN_DISPATCH(delta_scan_kernel, bf16, qkv, ldq, q_off, k_off, v_off, (const bf16*)ab, ldab, b_off, a_off, A_log, dt_bias, p_dtype, state, state_stride, spans, tok_slot, out, H, Hk, d, dv, unit_eps, q_scale)
+    } else {
+        GI_REQUIRE(false, "gi_delta_scan: activation dtype %d", act_dtype);
+    }
+    return gi_check_launch("gi_delta_scan");
+}

@@ -30,7 +30,8 @@ def _part_wants(spec: PartSpec) -> dict[str, TensorWant]:
 def plan_part_specs(plan: ModelPlan) -> list[PartSpec]:
     specs = [plan.embedding, *plan.positions.values()]
     for layer in plan.layers:
-        specs += [layer.mixer, layer.feed_forward, *layer.norms.values()]
+        specs += [layer.mixer, *([layer.feed_forward] if layer.feed_forward is not None else []),
+                  *layer.norms.values(), *layer.gates.values()]
     return specs + [plan.final_norm, plan.head]
 
 
@@ -84,9 +85,11 @@ class DecoderModel:
                 raise KeyError(f"layer {i} names position encoding {layer.position!r}; the plan has "
                                f"{sorted(self.positions)}")
             block_cls = part_class(layer.block)
-            self.blocks.append(block_cls(make(layer.mixer), make(layer.feed_forward),
+            extra = {"gates": {n: make(s) for n, s in layer.gates.items()}} if layer.gates else {}
+            self.blocks.append(block_cls(make(layer.mixer),
+                                         make(layer.feed_forward) if layer.feed_forward is not None else None,
                                          {n: make(s) for n, s in layer.norms.items()},
-                                         self.positions.get(layer.position), rt))
+                                         self.positions.get(layer.position), rt, **extra))
         self.final_norm = make(plan.final_norm)
         self.head = make(plan.head)
         self.schedule = tuple(plan.schedule)
@@ -154,6 +157,7 @@ class DecoderModel:
         yield self.embedding
         yield from self.positions.values()
         for b in self.blocks:
-            yield from (b.mixer, b.feed_forward, *[v for v in vars(b).values() if hasattr(v, "add_norm")])
+            yield from (p for p in (b.mixer, b.feed_forward) if p is not None)
+            yield from (v for v in vars(b).values() if hasattr(v, "add_norm") or hasattr(v, "logits"))
         yield self.final_norm
         yield self.head

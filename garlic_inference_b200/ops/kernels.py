@@ -178,23 +178,194 @@ def qk_norm_rope_append(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
 
 def attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
                       tok_pos: torch.Tensor, tok_slot: torch.Tensor, scale: float, window: int,
-                      status: torch.Tensor) -> torch.Tensor:
-    """Exact-order attention of q [n, n_q, d] over the paged cache; returns [n, n_q * d]."""
+                      status: torch.Tensor, sinks: Optional[torch.Tensor] = None,
+                      value_dim: Optional[int] = None) -> torch.Tensor:
+    """Exact-order attention of q [n, n_q, d] over the paged cache; returns [n, n_q * value_dim] (value_dim = d
+    unless given: the first columns of the value rows).  `sinks` [n_q]: a number per head that joins the
+    softmax's denominator as exp(sink), without a value."""
     l = require_gpu()
     _dense(q, "q")
     n, n_q, d = q.shape
+    d_v = d if value_dim is None else int(value_dim)
+    if sinks is not None:
+        _dense(sinks, "sinks")
+        if sinks.numel() != n_q:
+            raise KernelError(f"{sinks.numel()} sinks for {n_q} query heads")
     _dense(k_pool, "k_pool", q.dtype), _dense(v_pool, "v_pool", q.dtype)
     n_pages, n_kv, page_size, pool_d = k_pool.shape
     if pool_d != d or v_pool.shape != k_pool.shape:
         raise KernelError(f"cache pools {tuple(k_pool.shape)} do not fit head_dim {d}")
     for t, name in ((tok_pos, "tok_pos"), (tok_slot, "tok_slot"), (block_table, "block_table"), (status, "status")):
         _dense(t, name, torch.int32)
-    out = torch.empty((n, n_q * d), dtype=q.dtype, device=q.device)
+    out = torch.empty((n, n_q * d_v), dtype=q.dtype, device=q.device)
     check(l.gi_attention_generic(_ptr(q), _ptr(k_pool), _ptr(v_pool), code(q.dtype), _ptr(block_table),
                                  _ptr(tok_pos), _ptr(tok_slot), _ptr(out), n, n_q, n_kv, d, page_size,
-                                 block_table.shape[1], n_pages, int(window or 0), float(scale), _ptr(status),
-                                 _stream()), l)
+                                 block_table.shape[1], n_pages, int(window or 0), float(scale), _ptr(sinks),
+                                 code(sinks.dtype) if sinks is not None else F32, d_v, _ptr(status), _stream()), l)
     return out
+
+
+def _rows(t: torch.Tensor, name: str, dtype=None) -> torch.Tensor:
+    """A 2-D tensor whose rows are dense but may lie apart (columns of a wider product's output)."""
+    if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"{name} of shape {tuple(t.shape)} and strides {t.stride()} is no matrix of dense rows on the GPU")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} is {t.dtype}, the kernel wants {dtype}")
+    return t
+
+
+def gate_norm_add(y: torch.Tensor, gate: Optional[torch.Tensor], bias: Optional[torch.Tensor], weight: torch.Tensor,
+                  eps: float, residual: torch.Tensor, want_copy: bool) -> Optional[torch.Tensor]:
+    """residual += rmsnorm(y * sigmoid(gate + bias)) * weight, all in float32 (without `gate`: the norm of y
+    itself).  With `want_copy` returns the new residual rounded to y's type, for the next products."""
+    l = require_gpu()
+    act = y.dtype
+    _rows(y, "y"), _dense(residual, "residual", torch.float32), _dense(weight, "weight")
+    n, dim = y.shape
+    if residual.shape != (n, dim) or weight.numel() != dim:
+        raise KernelError(f"y {tuple(y.shape)}, residual {tuple(residual.shape)} and a norm weight of {weight.numel()} differ")
+    if gate is not None:
+        _rows(gate, "gate", act)
+        if gate.shape != (n, dim) or (bias is not None and _dense(bias, "bias").numel() != dim):
+            raise KernelError(f"gate {tuple(gate.shape)} / bias do not fit rows of {dim}")
+    copy = torch.empty((n, dim), dtype=act, device=y.device) if want_copy else None
+    check(l.gi_gate_norm_add(_ptr(y), y.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(bias),
+                             code(bias.dtype) if bias is not None else F32, _ptr(weight), code(weight.dtype),
+                             _ptr(residual), _ptr(copy), code(act), n, dim, float(eps), _stream()), l)
+    return copy
+
+
+def xielu(z: torch.Tensor, pq: torch.Tensor) -> torch.Tensor:
+    """softplus(p) z^2 + z/2 for z > 0, (1/2 + softplus(q)) (e^z - 1 - z) + z/2 otherwise; pq = [p, q] on the device."""
+    l = require_gpu()
+    _rows(z, "z"), _dense(pq, "pq")
+    if pq.numel() != 2:
+        raise KernelError(f"xielu takes two numbers, not {pq.numel()}")
+    n, cols = z.shape
+    out = torch.empty((n, cols), dtype=z.dtype, device=z.device)
+    check(l.gi_xielu(_ptr(z), z.stride(0), _ptr(out), code(z.dtype), _ptr(pq), code(pq.dtype), n, cols, _stream()), l)
+    return out
+
+
+def gated_group_rmsnorm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, groups: int,
+                        gate_kind: str) -> torch.Tensor:
+    """o float32 [n, groups * gs]: each group divided by its root mean square, times weight (one per column, or
+    one per column of a group), times sigmoid(gate) or silu(gate); returns gate's type."""
+    l = require_gpu()
+    _dense(o, "o", torch.float32), _rows(gate, "gate"), _dense(weight, "weight")
+    n, cols = o.shape
+    if cols % groups or gate.shape != (n, cols):
+        raise KernelError(f"o {tuple(o.shape)} in {groups} groups, gate {tuple(gate.shape)}")
+    out = torch.empty((n, cols), dtype=gate.dtype, device=o.device)
+    check(l.gi_gated_group_rmsnorm(_ptr(o), _ptr(gate), gate.stride(0), _ptr(weight), code(weight.dtype), weight.numel(),
+                                   _ptr(out), code(gate.dtype), n, groups, cols // groups, float(eps),
+                                   {"sigmoid": 0, "silu": 1}[gate_kind], _stream()), l)
+    return out
+
+
+def scan_state_floats(key_dim: int, value_dim: int) -> int:
+    """Floats of one head's recurrent state as the scan kernels lay it out (keys padded for their loads)."""
+    from .library import lib
+    n = lib().gi_scan_state_floats(int(key_dim), int(value_dim))
+    if n < 0:
+        raise KernelError(f"a key dimension of {key_dim} is beyond the scan kernels' 256")
+    return int(n)
+
+
+def causal_conv_silu(x: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, tok_slot: torch.Tensor) -> torch.Tensor:
+    """silu of the causal convolution over time of x [n, C] (rows may lie apart) with taps [C, K], the K-1 inputs
+    before the step's first token of a sequence taken from `state` [slots, >= (K-1) C] (a view of float32 state
+    rows); returns float32 [n, C].  Call `conv_state_update` afterwards."""
+    l = require_gpu()
+    _rows(x, "x"), _dense(taps, "taps"), _rows(state, "state", torch.float32), _dense(tok_slot, "tok_slot", torch.int32)
+    n, C = x.shape
+    out = torch.empty((n, C), dtype=torch.float32, device=x.device)
+    check(l.gi_causal_conv_silu(_ptr(x), x.stride(0), code(x.dtype), C, _ptr(taps), code(taps.dtype), taps.shape[1],
+                                _ptr(state), state.stride(0), _ptr(tok_slot), _ptr(out), n, 0, _stream()), l)
+    return out
+
+
+def conv_state_update(x: torch.Tensor, n_taps: int, state: torch.Tensor, tok_slot: torch.Tensor) -> None:
+    """Each sequence's state becomes the last K-1 inputs it has seen (this step's rows, then what the state held)."""
+    l = require_gpu()
+    _rows(x, "x"), _rows(state, "state", torch.float32), _dense(tok_slot, "tok_slot", torch.int32)
+    if n_taps <= 1:
+        return
+    check(l.gi_causal_conv_silu(_ptr(x), x.stride(0), code(x.dtype), x.shape[1], None, F32, n_taps, _ptr(state),
+                                state.stride(0), _ptr(tok_slot), None, x.shape[0], 1, _stream()), l)
+
+
+def _scan_args(spans: Optional[torch.Tensor], tok_slot: torch.Tensor, n_rows: int):
+    _dense(tok_slot, "tok_slot", torch.int32)
+    if spans is None:
+        return None, n_rows
+    _dense(spans, "spans", torch.int32)
+    if spans.dim() != 2 or spans.shape[1] != 3:
+        raise KernelError(f"spans of shape {tuple(spans.shape)}, not [sequences, 3]")
+    return spans, spans.shape[0]
+
+
+def decay_scan(qkv: torch.Tensor, offsets: tuple, decay: torch.Tensor, state: torch.Tensor,
+               spans: Optional[torch.Tensor], tok_slot: torch.Tensor, n_heads: int, key_dim: int,
+               value_dim: int) -> torch.Tensor:
+    """Linear attention with a fixed decay per head over the step's rows, from and to `state` [slots, floats]:
+    S = decay S + silu(k) silu(v)^T, o = S^T silu(q).  q, k, v are columns of `qkv` at `offsets`.  `spans`
+    [n_seq, 3] = {slot, first row, rows}; None: every row is a sequence of its own (slot from tok_slot).
+    Returns float32 [n, n_heads * value_dim]."""
+    l = require_gpu()
+    _rows(qkv, "qkv"), _dense(decay, "decay", torch.float32), _rows(state, "state", torch.float32)
+    n = qkv.shape[0]
+    spans, n_seq = _scan_args(spans, tok_slot, n)
+    out = torch.empty((n, n_heads * value_dim), dtype=torch.float32, device=qkv.device)
+    check(l.gi_decay_scan(_ptr(qkv), qkv.stride(0), code(qkv.dtype), *map(int, offsets), _ptr(decay), _ptr(state),
+                          state.stride(0), _ptr(spans), _ptr(tok_slot), _ptr(out), n_seq, n_heads, key_dim, value_dim,
+                          _stream()), l)
+    return out
+
+
+def delta_scan(qkv: torch.Tensor, offsets: tuple, ab: torch.Tensor, ab_offsets: tuple, A_log: torch.Tensor,
+               dt_bias: torch.Tensor, state: torch.Tensor, spans: Optional[torch.Tensor], tok_slot: torch.Tensor,
+               n_heads: int, n_kv_heads: int, key_dim: int, value_dim: int, unit_eps: float) -> torch.Tensor:
+    """The gated delta rule over the step's rows, from and to `state`.  `qkv` float32 [n, C] holds q, k (per key
+    head) and v (per head) at `offsets`; `ab` holds the logits of beta and of the decay at `ab_offsets` (one
+    column per head).  Returns float32 [n, n_heads * value_dim]."""
+    l = require_gpu()
+    _rows(qkv, "qkv", torch.float32), _rows(ab, "ab"), _rows(state, "state", torch.float32)
+    _dense(A_log, "A_log"), _dense(dt_bias, "dt_bias", A_log.dtype)
+    n = qkv.shape[0]
+    spans, n_seq = _scan_args(spans, tok_slot, n)
+    out = torch.empty((n, n_heads * value_dim), dtype=torch.float32, device=qkv.device)
+    check(l.gi_delta_scan(_ptr(qkv), qkv.stride(0), *map(int, offsets), _ptr(ab), ab.stride(0), code(ab.dtype),
+                          *map(int, ab_offsets), _ptr(A_log), _ptr(dt_bias), code(A_log.dtype), _ptr(state),
+                          state.stride(0), _ptr(spans), _ptr(tok_slot), _ptr(out), n_seq, n_heads, n_kv_heads,
+                          key_dim, value_dim, float(unit_eps), float(key_dim) ** -0.5, _stream()), l)
+    return out
+
+
+def latent_prepare(proj: torch.Tensor, q_off: int, c_off: int, q_lat: torch.Tensor, norm_w: torch.Tensor, eps: float,
+                   freq: torch.Tensor, magnitude: float, n_rot: int, tok_pos: torch.Tensor, tok_slot: torch.Tensor,
+                   block_table: torch.Tensor, pool: torch.Tensor, n_heads: int, plain_dim: int, rot_dim: int,
+                   rank: int, status: torch.Tensor, append: bool = True) -> torch.Tensor:
+    """Latent attention between projections and attention: writes each token's cache row [normed latent | rotated
+    shared key part | zeros] into `pool` [pages, 1, page_size, row] and returns the queries [n, heads, row] =
+    [q' | rotated part | zeros], q' = `q_lat` [n, heads, rank]."""
+    l = require_gpu()
+    act = proj.dtype
+    _rows(proj, "proj"), _dense(q_lat, "q_lat", act), _dense(norm_w, "norm_w"), _dense(freq, "freq", torch.float32)
+    _dense(pool, "pool", act)
+    for t, name in ((tok_pos, "tok_pos"), (tok_slot, "tok_slot"), (block_table, "block_table"), (status, "status")):
+        _dense(t, name, torch.int32)
+    n = proj.shape[0]
+    n_pages, one, page_size, row_w = pool.shape
+    if one != 1 or q_lat.shape != (n, n_heads, rank) or norm_w.numel() != rank or freq.numel() * 2 != n_rot:
+        raise KernelError("latent_prepare: the pool, q_lat, the norm weight or the frequencies do not fit the sizes")
+    q_out = torch.empty((n, n_heads, row_w), dtype=act, device=proj.device)
+    check(l.gi_latent_prepare(_ptr(proj), proj.stride(0), q_off, c_off, _ptr(q_lat), code(act), _ptr(norm_w),
+                              code(norm_w.dtype), float(eps), _ptr(freq), float(magnitude), n_rot, _ptr(tok_pos),
+                              _ptr(tok_slot), _ptr(block_table), _ptr(pool), _ptr(q_out), n, n_heads, plain_dim,
+                              rot_dim, rank, row_w, page_size, block_table.shape[1], n_pages, int(append),
+                              _ptr(status), _stream()), l)
+    return q_out
 
 
 def sgemm_nt(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -208,6 +379,18 @@ def sgemm_nt(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = Non
         out = torch.empty((m, n), dtype=torch.float32, device=a.device)
     _dense(out, "out", torch.float32)
     check(l.gi_sgemm_nt(_ptr(a), _ptr(w), _ptr(out), m, n, k, k, n, _stream()), l)
+    return out
+
+
+def sgemm_nt_strided(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """a [M,K] . w[N,K]^T in true float32 into `out` [M,N]; the rows of a and of out may lie apart."""
+    l = require_gpu()
+    _rows(a, "a", torch.float32), _dense(w, "w", torch.float32), _rows(out, "out", torch.float32)
+    (m, k), (n, k2) = a.shape, w.shape
+    if k != k2 or out.shape != (m, n):
+        raise KernelError(f"a {tuple(a.shape)}, w {tuple(w.shape)} and out {tuple(out.shape)} do not fit")
+    check(l.gi_sgemm_nt(_ptr(a), _ptr(w), _ptr(out), m, n, k, a.stride(0) if m > 1 else k,
+                        out.stride(0) if m > 1 else n, _stream()), l)
     return out
 
 

@@ -112,3 +112,25 @@ def swiglu_product(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
             return kernels.gemv_swiglu_bf16(x, w_gate_up)
         return kernels.gemm_skinny_swiglu_bf16(x, w_gate_up)
     return kernels.swiglu(linear(x, w_gate_up))
+
+
+def per_head_linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """y[n, h, :] = w[h] x[n, h, :] for a weight [heads, out, in] and x [n, heads, in], whose heads and rows may lie
+    apart (columns of a wider product's output) while each head's `in` values are dense; returns dense
+    [n, heads, out].  float32: this package's float32 kernel, head by head, reading and writing in place;
+    bfloat16: the library's batched product (float32 accumulation)."""
+    if x.dim() != 3 or w.dim() != 3 or x.shape[1] != w.shape[0] or x.shape[2] != w.shape[2] or x.stride(2) != 1:
+        raise KernelError(f"per_head_linear: x {tuple(x.shape)} (strides {x.stride()}) does not fit a weight {tuple(w.shape)}")
+    n, heads, k = x.shape
+    m = w.shape[1]
+    if w.dtype == torch.float32:
+        if x.dtype != torch.float32:
+            raise KernelError(f"per_head_linear: a float32 weight takes float32 activations, not {x.dtype}")
+        out = torch.empty((n, heads, m), dtype=torch.float32, device=x.device)
+        for h in range(heads):
+            kernels.sgemm_nt_strided(x[:, h], w[h], out[:, h])
+        return out
+    if w.dtype != torch.bfloat16 or x.dtype != torch.bfloat16:
+        raise KernelError(f"per_head_linear: weight {w.dtype}, activations {x.dtype}")
+    kernels.require_gpu()
+    return torch.bmm(x.transpose(0, 1), w.transpose(1, 2)).transpose(0, 1).contiguous()

@@ -1,12 +1,16 @@
 """Parts a model is put together from; importing this package registers the built-in ones."""
-from .base import (Block, Embedding, FeedForward, Head, Mixer, Norm, Part, PositionEncoding, Runtime,
+from .base import (Block, Embedding, FeedForward, Gate, Head, Mixer, Norm, Part, PositionEncoding, Runtime,
                    StepContext, StepShape, known_parts, part_class, register_part)
 from .attention import GQAAttention
-from .block import LinearHead, PreNormResidualBlock, TokenEmbedding
-from .mlp import SwiGLUMLP
+from .block import LinearHead, PostNormGatedResidualBlock, PreNormResidualBlock, SigmoidGate, TokenEmbedding
+from .delta_rule import GatedDeltaRule
+from .latent_attention import LatentAttention
+from .linear_attention import DecayLinearAttention
+from .mlp import SwiGLUMLP, XieluMLP
 from .norm import RMSNorm
 from .rotary import RotaryPositions
 
-__all__ = ["Block", "Embedding", "FeedForward", "Head", "Mixer", "Norm", "Part", "PositionEncoding",
+__all__ = ["Block", "Embedding", "FeedForward", "Gate", "Head", "PostNormGatedResidualBlock", "SigmoidGate",
+           "GatedDeltaRule", "LatentAttention", "DecayLinearAttention", "XieluMLP", "Mixer", "Norm", "Part", "PositionEncoding",
            "Runtime", "StepContext", "StepShape", "known_parts", "part_class", "register_part", "GQAAttention",
            "LinearHead", "PreNormResidualBlock", "TokenEmbedding", "SwiGLUMLP", "RMSNorm", "RotaryPositions"]

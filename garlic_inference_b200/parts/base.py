@@ -14,6 +14,7 @@ register the class and name its kind in a plan.
     class Norm(Part)             add_norm(delta, residual, ...) -> normed                 [n, size]
     class PositionEncoding(Part) rotary_tables() / on_embedding(residual, ctx)
     class Block(Part)            step(delta, residual, ctx, cache, writes_cache) -> delta
+    class Gate(Part)             logits(x) -> [n, hidden]; the arrangement applies sigmoid(logits + bias)
     class Embedding(Part)        step(ctx) -> residual (float32)
     class Head(Part)             step(normed_rows) -> logits (float32)
 
@@ -101,6 +102,30 @@ class StepContext:
     status: Optional[torch.Tensor] = None   # int32[1] error flag shared with the cache
     captured: bool = False              # the step is being recorded into a CUDA graph: the host-side
                                         # lists above are empty, everything must come from the tensors
+    # The residual stream rounded to the activation type, when the block that ran last left one beside the
+    # float32 stream (blocks whose sublayers read the stream itself hand it from one to the next; any block
+    # that changes the stream without renewing this copy sets it back to None).
+    residual_act: Optional[torch.Tensor] = None
+
+    def seq_spans(self) -> Optional[torch.Tensor]:
+        """int32 [n_seq, 3] = {slot, first row, rows} on the device for kernels that walk each sequence's rows
+        in order, or None when every row is a sequence of its own (decode steps; the slot is tok_slot's)."""
+        if self.all_single:
+            return None
+        spans = self.arrays.get("seq_spans")
+        if spans is None:                     # a context put together by hand: make and copy here
+            import numpy as np
+            spans = torch.from_numpy(seq_spans_array(self)).to(self.tok_pos.device)
+            self.arrays["seq_spans"] = spans
+        return spans
+
+
+def seq_spans_array(shape):
+    """{slot, first row, rows} of each sequence of a step as int32 [n_seq, 3]; the longest first, so that the
+    blocks that run longest start first."""
+    import numpy as np
+    spans = sorted(zip(shape.seq_slots, shape.seq_starts, shape.seq_lens), key=lambda t: -t[2])
+    return np.asarray(spans, dtype=np.int32).reshape(-1, 3)
 
 
 class Part:
@@ -155,6 +180,11 @@ class PositionEncoding(Part):
 
     def on_embedding(self, residual, ctx: StepContext) -> None:
         """Hook for encodings that act on the embedded tokens (learned absolute positions)."""
+
+
+class Gate(Part):
+    def logits(self, x):
+        raise NotImplementedError
 
 
 class Block(Part):

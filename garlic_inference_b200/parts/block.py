@@ -4,6 +4,14 @@
     r = h;  x = norm_in(h);  r = mixer(x) + r;  x = norm_post(r);  h = ffn(x) + r
 The residual stream is float32; each add happens inside the norm that
 follows it, so the block takes and returns a pending `delta` (see base.py).
+
+`post_norm_gated_residual` (no upstream counterpart): the sublayers read the
+stream itself and the norm sits on each sublayer's result, behind a gate that
+is made from the sublayer's input:
+    h += norm_mixer( sigmoid(G1 h + b1) * mixer(h) );  h += norm_ff( sigmoid(G2 h + b2) * ffn(h) )
+Gate, norm and add are one float32 kernel, which also leaves the new stream
+in the activation type for the products that read it next; nothing is pending
+when the block returns.  The feed-forward and either gate may be absent.
 """
 from __future__ import annotations
 
@@ -11,7 +19,7 @@ import torch
 
 from ..ops import kernels, linear
 from ..weights.loader import TensorWant
-from .base import Block, Embedding, Head, register_part
+from .base import Block, Embedding, Gate, Head, register_part
 
 
 class PreNormResidualBlock(Block):
@@ -38,10 +46,83 @@ class PreNormResidualBlock(Block):
         return {**self.mixer.step_arrays(shape, cache), **self.feed_forward.step_arrays(shape, cache)}
 
     def step(self, delta, residual, ctx, cache, writes_cache=True):
+        ctx.residual_act = None                     # this block changes the stream and keeps no rounded copy
         x = self.norm_in.add_norm(delta, residual)
         a = self.mixer.step(x, ctx, cache, self.position, writes_cache)
         x = self.norm_post.add_norm(a, residual)
         return self.feed_forward.step(x, ctx)
+
+
+class SigmoidGate(Gate):
+    """A gate on a sublayer's result, one number per channel: sigmoid(W x + b) with x the sublayer's input.
+    This part owns W and b and makes the logits; the arrangement's kernel adds b and applies the sigmoid in
+    float32 where it multiplies."""
+    kind = "sigmoid_gate"
+    graph_safe = True
+
+    @classmethod
+    def wanted(cls, params):
+        h = params["hidden_size"]
+        return {"weight": TensorWant((h, h)), "bias": TensorWant((h,))}
+
+    def __init__(self, params, load, rt):
+        super().__init__(params, load, rt)
+        self.weight, self.bias = load("weight"), load("bias")
+
+    def logits(self, x):
+        return linear(x, self.weight)
+
+
+class PostNormGatedResidualBlock(Block):
+    kind = "post_norm_gated_residual"
+
+    def __init__(self, mixer, feed_forward, norms, position, rt, gates=None):
+        self.rt = rt
+        self.mixer, self.feed_forward, self.position = mixer, feed_forward, position
+        gates = gates or {}
+        need = ["post_mixer"] + (["post_ff"] if feed_forward is not None else [])
+        missing = [n for n in need if n not in norms]
+        if missing:
+            raise ValueError(f"block 'post_norm_gated_residual' needs norms {need}; missing {missing}")
+        self.norm_mixer, self.norm_ff = norms["post_mixer"], norms.get("post_ff")
+        self.gate_mixer, self.gate_ff = gates.get("mixer"), gates.get("ff")
+
+    def cache_requirement(self):
+        return self.mixer.cache_requirement()
+
+    @property
+    def graph_safe(self):
+        parts = (self.mixer, self.feed_forward, self.norm_mixer, self.norm_ff, self.gate_mixer, self.gate_ff,
+                 self.position)
+        return all(p.graph_safe for p in parts if p is not None)
+
+    def step_arrays(self, shape, cache):
+        ff = self.feed_forward.step_arrays(shape, cache) if self.feed_forward is not None else {}
+        return {**self.mixer.step_arrays(shape, cache), **ff}
+
+    def _join(self, y, gate, norm, x, residual, want_copy):
+        g = gate.logits(x) if gate is not None else None
+        return kernels.gate_norm_add(y, g, gate.bias if gate is not None else None, norm.weight, norm.eps, residual,
+                                     want_copy)
+
+    def step(self, delta, residual, ctx, cache, writes_cache=True):
+        act = self.rt.dtype
+        if delta is not None:                       # a block before this one left its result pending
+            kernels.residual_add(delta, residual)
+            ctx.residual_act = None
+        # the stream in the activation type: the stream itself under float32, else the copy the last
+        # gate-norm-add kernel wrote, else a cast
+        copies = act != torch.float32
+        x = residual if not copies else (ctx.residual_act if ctx.residual_act is not None
+                                         else kernels.cast(residual, act))
+        y = self.mixer.step(x, ctx, cache, self.position, writes_cache)
+        x2 = self._join(y, self.gate_mixer, self.norm_mixer, x, residual, copies)
+        x = x2 if copies else residual
+        if self.feed_forward is not None:
+            y = self.feed_forward.step(x, ctx)
+            x2 = self._join(y, self.gate_ff, self.norm_ff, x, residual, copies)
+        ctx.residual_act = x2 if copies else None
+        return None
 
 
 class TokenEmbedding(Embedding):
@@ -79,5 +160,7 @@ class LinearHead(Head):
 
 
 register_part(PreNormResidualBlock.kind, PreNormResidualBlock)
+register_part(PostNormGatedResidualBlock.kind, PostNormGatedResidualBlock)
+register_part(SigmoidGate.kind, SigmoidGate)
 register_part(TokenEmbedding.kind, TokenEmbedding)
 register_part(LinearHead.kind, LinearHead)

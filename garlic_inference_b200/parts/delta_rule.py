@@ -1,0 +1,79 @@
+"""The gated delta rule behind short causal convolutions, as a mixer with a matrix of state per head.
+
+    q, k, v = silu(conv(Wq x)), silu(conv(Wk x)), silu(conv(Wv x))     conv: per channel over time, `conv_taps`
+                                                                        taps, the last on the current token
+    q, k <- q / sqrt(|q|^2 + unit_eps) * key_dim^-1/2,  k / sqrt(|k|^2 + unit_eps)        per head
+    beta = sigmoid(Wb x),   g = exp(-exp(A_h) softplus(Wa x + dt_h))                        one per head
+    S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q       float32; the read-out sees this token's write
+    y = Wo( o / rms(o over value_dim) * w * silu(Wg x) )
+
+q and k have `n_kv_heads` heads; head h of v reads q/k head h // (n_heads // n_kv_heads).  The six projections
+that read x are one packed product.  A slot's state row holds the matrices of all heads and, behind them, the
+last conv_taps - 1 inputs of the convolutions.  Upstream has no recurrent mixer.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache import StateRequirement
+from ..ops import kernels, linear
+from ..weights.loader import TensorWant
+from .base import Mixer, register_part, seq_spans_array
+from .linear_attention import pack_rows, scan_state_floats
+
+
+class GatedDeltaRule(Mixer):
+    kind = "gated_delta_rule"
+    graph_safe = True
+
+    @classmethod
+    def wanted(cls, params):
+        hid, H, Hk, d, dv, K = (params[k] for k in ("hidden_size", "n_heads", "n_kv_heads", "key_dim", "value_dim",
+                                                    "conv_taps"))
+        taps = lambda rows: TensorWant((rows, K), std_scale=8.0)
+        return {"q": TensorWant((Hk * d, hid)), "k": TensorWant((Hk * d, hid)), "v": TensorWant((H * dv, hid)),
+                "q.conv": taps(Hk * d), "k.conv": taps(Hk * d), "v.conv": taps(H * dv),
+                "b": TensorWant((H, hid)), "a": TensorWant((H, hid)), "A_log": TensorWant((H,)),
+                "dt_bias": TensorWant((H,)), "g": TensorWant((H * dv, hid)), "o": TensorWant((hid, H * dv)),
+                "norm": TensorWant((dv,), "norm")}
+
+    def __init__(self, params, load, rt):
+        super().__init__(params, load, rt)
+        self.hidden, self.H, self.Hk = int(params["hidden_size"]), int(params["n_heads"]), int(params["n_kv_heads"])
+        self.d, self.dv, self.K = int(params["key_dim"]), int(params["value_dim"]), int(params["conv_taps"])
+        self.eps, self.unit_eps = float(params["eps"]), float(params.get("unit_eps", 1e-6))
+        if self.H % self.Hk:
+            raise ValueError(f"{self.H} heads are no multiple of {self.Hk} key heads")
+        self.w_in, offs = pack_rows(load, (("q", self.Hk * self.d), ("k", self.Hk * self.d), ("v", self.H * self.dv),
+                                            ("g", self.H * self.dv), ("b", self.H), ("a", self.H)), self.hidden, rt)
+        self.q_off, self.k_off, self.v_off, self.g_off, self.b_off, self.a_off = offs
+        self.C = 2 * self.Hk * self.d + self.H * self.dv              # channels that pass the convolution
+        self.taps = torch.cat([load("q.conv"), load("k.conv"), load("v.conv")]).contiguous()
+        self.A_log, self.dt_bias = load("A_log"), load("dt_bias")
+        self.w_o, self.norm = load("o"), load("norm")
+        self.scan_floats = self.H * scan_state_floats(self.d, self.dv)
+        self.state_floats = -(-(self.scan_floats + (self.K - 1) * self.C) // 4) * 4
+
+    def cache_requirement(self):
+        return StateRequirement((self.state_floats,), torch.float32)
+
+    def step_arrays(self, shape, cache):
+        return {} if shape.all_single else {"seq_spans": lambda: seq_spans_array(shape)}
+
+    def step(self, x, ctx, cache, position, writes_cache=True):
+        if not writes_cache:
+            raise ValueError("a mixer with state of its own cannot read another layer's")
+        proj = linear(x, self.w_in)
+        conv_in = proj[:, :self.C]
+        conv_state = cache.state[:, self.scan_floats:]
+        qkv = kernels.causal_conv_silu(conv_in, self.taps, conv_state, ctx.tok_slot)
+        kernels.conv_state_update(conv_in, self.K, conv_state, ctx.tok_slot)
+        o = kernels.delta_scan(qkv, (self.q_off, self.k_off, self.v_off), proj, (self.b_off, self.a_off), self.A_log,
+                               self.dt_bias, cache.state, ctx.seq_spans(), ctx.tok_slot, self.H, self.Hk, self.d,
+                               self.dv, self.unit_eps)
+        y = kernels.gated_group_rmsnorm(o, proj[:, self.g_off:self.g_off + self.H * self.dv], self.norm, self.eps,
+                                        groups=self.H, gate_kind="silu")
+        return linear(y, self.w_o)
+
+
+register_part(GatedDeltaRule.kind, GatedDeltaRule)

@@ -1,0 +1,89 @@
+"""Attention whose keys and values are expanded from a cached low-rank latent, as a mixer.
+
+    q = Wq x = per head [ plain_dim unrotated | rot_dim rotated ]
+    [c | kr] = Wdkv x;  c <- rmsnorm(c) * w  (kv_rank);  kr (rot_dim): one rotated key part shared by all heads
+    head h:  key = [ Wuk,h c | rot(kr) ],  value = Wuv,h c
+    score = (q_plain . Wuk,h c + rot(q_rot) . rot(kr)) * softmax_scale,  causal
+    softmax whose denominator also holds exp(sink_h) (optional, one learned number per head)
+    y = Wo concat_h( sum_j p_j Wuv,h c_j )
+
+Only c and rot(kr) are cached: one row per position in a single-plane paged entry.  The expansion is never
+materialised: q'_h = Wuk,h^T q_plain,h is made by a per-head product, attention runs over the cached rows for
+all heads (score q'_h . c_j + rot(q_rot) . rot(kr_j), values c_j), and Wuv,h is applied to the result.  Scores,
+softmax and the weighted sum are float32 for prompts and single tokens alike (the exact-order kernel).
+The rotation is the position part's (its frequencies, magnitude and layout; this mixer's kernel pairs
+dimension 2i with 2i+1).  Upstream has grouped-query attention only (src/models/qwen3/qwen3.cpp:140-179).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache import KVRequirement
+from ..ops import kernels, linear, per_head_linear
+from ..weights.loader import TensorWant
+from .base import Mixer, register_part
+from .linear_attention import pack_rows
+
+
+class LatentAttention(Mixer):
+    kind = "latent_attention"
+    graph_safe = True
+
+    @classmethod
+    def wanted(cls, params):
+        hid, H, d, dr, dv, r = (params[k] for k in ("hidden_size", "n_heads", "plain_dim", "rot_dim", "value_dim",
+                                                    "kv_rank"))
+        w = {"q": TensorWant((H * (d + dr), hid)), "dkv": TensorWant((r + dr, hid)), "dkv.norm": TensorWant((r,), "norm"),
+             "uk": TensorWant((H * d, r)), "uv": TensorWant((H * dv, r)), "o": TensorWant((hid, H * dv))}
+        if params.get("sink", False):
+            w["sink"] = TensorWant((H,))
+        return w
+
+    def __init__(self, params, load, rt):
+        super().__init__(params, load, rt)
+        self.hidden, self.H = int(params["hidden_size"]), int(params["n_heads"])
+        self.d, self.dr, self.dv, self.rank = (int(params[k]) for k in ("plain_dim", "rot_dim", "value_dim", "kv_rank"))
+        self.scale, self.eps = float(params["softmax_scale"]), float(params["eps"])
+        self.row = -(-(self.rank + self.dr) // 8) * 8             # a cache row, padded for the kernel's 16-byte loads
+        self.w_in, (self.q_off, self.c_off) = pack_rows(
+            load, (("q", self.H * (self.d + self.dr)), ("dkv", self.rank + self.dr)), self.hidden, rt)
+        self.c_norm = load("dkv.norm")
+        # Wuk per head as [rank, plain_dim]: the product q'_h = Wuk,h^T q_h in the [out, in] form of the others
+        self.w_uk_t = load("uk").view(self.H, self.d, self.rank).transpose(1, 2).contiguous()
+        self.w_uv = load("uv").view(self.H, self.dv, self.rank)
+        self.w_o = load("o")
+        self.sink = load("sink") if params.get("sink", False) else None
+        self._no_rotation = None
+
+    def cache_requirement(self):
+        return KVRequirement(1, self.row, None, planes=1)
+
+    def _rotation(self, position, device):
+        if position is not None:
+            freq, magnitude, n_rot, layout = position.rotary_frequencies()
+            if layout != "interleaved":
+                raise ValueError("latent_attention rotates pairs (2i, 2i+1): the position part must be 'interleaved'")
+            if n_rot > self.dr:
+                raise ValueError(f"{n_rot} rotated dimensions of a key part of {self.dr}")
+            return freq, magnitude, n_rot
+        if self._no_rotation is None:
+            self._no_rotation = torch.zeros(0, dtype=torch.float32, device=device)
+        return self._no_rotation, 1.0, 0
+
+    def step(self, x, ctx, cache, position, writes_cache=True):
+        kv = cache.kv
+        n = x.shape[0]
+        freq, magnitude, n_rot = self._rotation(position, x.device)
+        proj = linear(x, self.w_in)
+        q = proj[:, self.q_off:self.q_off + self.H * (self.d + self.dr)].view(n, self.H, self.d + self.dr)
+        q_lat = per_head_linear(q[:, :, :self.d], self.w_uk_t)                       # [n, H, rank]
+        q_rows = kernels.latent_prepare(proj, self.q_off, self.c_off, q_lat, self.c_norm, self.eps, freq, magnitude,
+                                        n_rot, ctx.tok_pos, ctx.tok_slot, kv.block_table, kv.k_pool, self.H, self.d,
+                                        self.dr, self.rank, ctx.status, append=writes_cache)
+        o_lat = kernels.attention_generic(q_rows, kv.k_pool, kv.k_pool, kv.block_table, ctx.tok_pos, ctx.tok_slot,
+                                          self.scale, 0, ctx.status, sinks=self.sink, value_dim=self.rank)
+        o = per_head_linear(o_lat.view(n, self.H, self.rank), self.w_uv)             # [n, H, value_dim]
+        return linear(o.view(n, self.H * self.dv), self.w_o)
+
+
+register_part(LatentAttention.kind, LatentAttention)

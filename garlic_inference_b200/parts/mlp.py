@@ -1,4 +1,12 @@
-"""SwiGLU feed-forward: down( silu(gate(x)) * up(x) ), no biases
+"""Feed-forwards.
+
+`xielu_mlp`: down( a(up(x)) ), no biases, with the xIELU activation
+    a(z) = softplus(p) z^2 + z/2                         for z > 0
+           (1/2 + softplus(q)) (e^z - 1 - z) + z/2       for z <= 0
+whose two numbers (p, q) are a tensor of the layer; float32 inside, one
+rounding.  Upstream has no such feed-forward.
+
+`swiglu_mlp`, the SwiGLU feed-forward: down( silu(gate(x)) * up(x) ), no biases
 (src/models/qwen3/qwen3.cpp:186-203).  gate and up are packed into one weight
 at load time (one product instead of two); silu and the product are one kernel
 in float32 with a single rounding (upstream rounds after silu and again after
@@ -7,7 +15,7 @@ from __future__ import annotations
 
 import torch
 
-from ..ops import linear, swiglu_product
+from ..ops import kernels, linear, swiglu_product
 from ..weights.loader import TensorWant
 from .base import FeedForward, register_part
 
@@ -34,4 +42,22 @@ class SwiGLUMLP(FeedForward):
         return linear(swiglu_product(x, self.w_gate_up), self.w_down)
 
 
+class XieluMLP(FeedForward):
+    kind = "xielu_mlp"
+    graph_safe = True
+
+    @classmethod
+    def wanted(cls, params):
+        h, i = params["hidden_size"], params["intermediate_size"]
+        return {"up": TensorWant((i, h)), "down": TensorWant((h, i)), "act": TensorWant((2,))}
+
+    def __init__(self, params, load, rt):
+        super().__init__(params, load, rt)
+        self.w_up, self.w_down, self.act = load("up"), load("down"), load("act")
+
+    def step(self, x, ctx):
+        return linear(kernels.xielu(linear(x, self.w_up), self.act), self.w_down)
+
+
 register_part(SwiGLUMLP.kind, SwiGLUMLP)
+register_part(XieluMLP.kind, XieluMLP)

@@ -42,6 +42,8 @@ class SurplusTensorWarning(UserWarning):
 class TensorWant:
     shape: tuple
     role: str = "matrix"        # "matrix" | "norm" | "table": used by random initialisation
+    std_scale: float = 1.0      # random initialisation multiplies its spread by this (short filters, whose few
+                                # taps would otherwise give outputs far smaller than a projection's)
 
 
 class Checkpoint:

@@ -69,7 +69,7 @@ def normal_values(key: int, n: int, mean: float, std: float, start: int = 0) -> 
 def random_tensor(name: str, want: TensorWant, seed: int, std: float, norm_mean: float, norm_std: float,
                   dtype: torch.dtype, device="cpu") -> torch.Tensor:
     device = torch.device(device)
-    mean, dev = (norm_mean, norm_std) if want.role == "norm" else (0.0, std)
+    mean, dev = (norm_mean, norm_std) if want.role == "norm" else (0.0, std * want.std_scale)
     key = tensor_key(seed, name)
     if device.type == "cuda":
         from ..ops import kernels
