@@ -120,8 +120,13 @@ class FivitarConfig:
                    norm_eps=require(norm, "eps", float, where + ": norm"), layers=layers)
 
     def to_dict(self) -> dict:
+        layers = copy.deepcopy(self.layers)
+        for layer in layers:                          # an absent scaling stays absent
+            rot = layer["mixer"].get("rot")
+            if rot is not None and rot.get("scaling") is None:
+                rot.pop("scaling", None)
         return {"architecture": ARCHITECTURE, "vocab": self.vocab, "width": self.width,
-                "norm": {"eps": self.norm_eps}, "layers": copy.deepcopy(self.layers)}
+                "norm": {"eps": self.norm_eps}, "layers": layers}
 
     # ---- checks ----------------------------------------------------------------
     def validate(self) -> None:

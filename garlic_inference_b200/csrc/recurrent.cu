@@ -204,11 +204,13 @@ decay_scan_kernel(const T* __restrict__ qkv, long long ld, int q_off, int k_off,
 
 // ---- the gated delta rule
 // qkv: float32 [n, ldq] (the convolution's output): q of key head kh at q_off + kh d, k at k_off + kh d, v of
-// head h at v_off + h dv.  ab: T [n, ldab]: beta's logit of head h at column b_off + h, the decay's at a_off + h.
+// head h at v_off + h dv.  ab: float32 [n, ldab]: beta's logit of head h at column b_off + h, the decay's at
+// a_off + h (float32 whatever the activation type is: the decay's logit is multiplied by exp(A_h) and goes
+// through two exponentials, which would magnify a 16-bit rounding).
 template <typename T, int R>
 __global__ void __launch_bounds__(SCAN_THREADS)
 delta_scan_kernel(const float* __restrict__ qkv, long long ldq, int q_off, int k_off, int v_off,
-                  const T* __restrict__ ab, long long ldab, int b_off, int a_off,
+                  const float* __restrict__ ab, long long ldab, int b_off, int a_off,
                   const void* __restrict__ A_log, const void* __restrict__ dt_bias, int p_dtype,
                   float* __restrict__ state, long long state_stride, const int* __restrict__ spans,
                   const int* __restrict__ tok_slot, float* __restrict__ out, int H, int Hk, int d, int dv,
@@ -257,9 +259,9 @@ delta_scan_kernel(const float* __restrict__ qkv, long long ldq, int q_off, int k
             const float iq = q_scale / sqrtf(sq + unit_eps), ik = 1.f / sqrtf(sk + unit_eps);
             for (int c = lane; c < DP; c += 32) { q_s[t][c] *= iq; k_s[t][c] *= ik; }
             if (lane == 0) {
-                const T* abr = ab + (size_t)(start + t0 + t) * ldab;
-                g_s[t] = expf(-rate * rc_softplus(to_f32(abr[a_off + h]) + dt));
-                b_s[t] = rc_sigmoid(to_f32(abr[b_off + h]));
+                const float* abr = ab + (size_t)(start + t0 + t) * ldab;
+                g_s[t] = expf(-rate * rc_softplus(abr[a_off + h] + dt));
+                b_s[t] = rc_sigmoid(abr[b_off + h]);
             }
             v_s[t][lane] = v0 + lane < dv ? row[v_off + h * dv + v0 + lane] : 0.f;
         }
@@ -342,8 +344,8 @@ extern "C" int gi_decay_scan(const void* qkv, long long ld, int act_dtype, int q
     return gi_check_launch("gi_decay_scan");
 }
 
-extern "C" int gi_delta_scan(const float* qkv, long long ldq, int q_off, int k_off, int v_off, const void* ab,
-                             long long ldab, int act_dtype, int b_off, int a_off, const void* A_log, const void* dt_bias,
+extern "C" int gi_delta_scan(const float* qkv, long long ldq, int q_off, int k_off, int v_off, const float* ab,
+                             long long ldab, int b_off, int a_off, const void* A_log, const void* dt_bias,
                              int p_dtype, float* state, long long state_stride, const int* spans, const int* tok_slot,
                              float* out, int n_seq, int H, int Hk, int d, int dv, float unit_eps, float q_scale,
                              void* stream) {
@@ -356,12 +358,6 @@ extern "C" int gi_delta_scan(const float* qkv, long long ldq, int q_off, int k_o
     if (n_seq == 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_seq, H, (dv + SCAN_VS - 1) / SCAN_VS);
-    if (act_dtype == GI_DTYPE_F32) {
-        SCAN_DISPATCH(delta_scan_kernel, float, qkv, ldq, q_off, k_off, v_off, (const float*)ab, ldab, b_off, a_off, A_log, dt_bias, p_dtype, state, state_stride, spans, tok_slot, out, H, Hk, d, dv, unit_eps, q_scale)
-    } else if (act_dtype == GI_DTYPE_BF16) {
-        SCAN_DISPATCH(delta_scan_kernel, bf16, qkv, ldq, q_off, k_off, v_off, (const bf16*)ab, ldab, b_off, a_off, A_log, dt_bias, p_dtype, state, state_stride, spans, tok_slot, out, H, Hk, d, dv, unit_eps, q_scale)
-    } else {
-        GI_REQUIRE(false, "gi_delta_scan: activation dtype %d", act_dtype);
-    }
+    SCAN_DISPATCH(delta_scan_kernel, float, qkv, ldq, q_off, k_off, v_off, ab, ldab, b_off, a_off, A_log, dt_bias, p_dtype, state, state_stride, spans, tok_slot, out, H, Hk, d, dv, unit_eps, q_scale)
     return gi_check_launch("gi_delta_scan");
 }

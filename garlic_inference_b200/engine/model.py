@@ -132,6 +132,7 @@ class DecoderModel:
     def forward(self, ctx: StepContext, cache, want_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """Run the step's tokens through every scheduled layer; float32 logits [n_wanted, vocab] at
         `want_rows` (int32 row indices), or None when nothing is wanted."""
+        ctx.residual_act = None                      # a context may be run again (recording a decode step)
         residual = self.embedding.step(ctx)
         for pos in self.positions.values():
             pos.on_embedding(residual, ctx)

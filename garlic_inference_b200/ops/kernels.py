@@ -327,15 +327,15 @@ def delta_scan(qkv: torch.Tensor, offsets: tuple, ab: torch.Tensor, ab_offsets: 
                dt_bias: torch.Tensor, state: torch.Tensor, spans: Optional[torch.Tensor], tok_slot: torch.Tensor,
                n_heads: int, n_kv_heads: int, key_dim: int, value_dim: int, unit_eps: float) -> torch.Tensor:
     """The gated delta rule over the step's rows, from and to `state`.  `qkv` float32 [n, C] holds q, k (per key
-    head) and v (per head) at `offsets`; `ab` holds the logits of beta and of the decay at `ab_offsets` (one
-    column per head).  Returns float32 [n, n_heads * value_dim]."""
+    head) and v (per head) at `offsets`; `ab` float32 holds the logits of beta and of the decay at `ab_offsets`
+    (one column per head).  Returns float32 [n, n_heads * value_dim]."""
     l = require_gpu()
-    _rows(qkv, "qkv", torch.float32), _rows(ab, "ab"), _rows(state, "state", torch.float32)
+    _rows(qkv, "qkv", torch.float32), _rows(ab, "ab", torch.float32), _rows(state, "state", torch.float32)
     _dense(A_log, "A_log"), _dense(dt_bias, "dt_bias", A_log.dtype)
     n = qkv.shape[0]
     spans, n_seq = _scan_args(spans, tok_slot, n)
     out = torch.empty((n, n_heads * value_dim), dtype=torch.float32, device=qkv.device)
-    check(l.gi_delta_scan(_ptr(qkv), qkv.stride(0), *map(int, offsets), _ptr(ab), ab.stride(0), code(ab.dtype),
+    check(l.gi_delta_scan(_ptr(qkv), qkv.stride(0), *map(int, offsets), _ptr(ab), ab.stride(0),
                           *map(int, ab_offsets), _ptr(A_log), _ptr(dt_bias), code(A_log.dtype), _ptr(state),
                           state.stride(0), _ptr(spans), _ptr(tok_slot), _ptr(out), n_seq, n_heads, n_kv_heads,
                           key_dim, value_dim, float(unit_eps), float(key_dim) ** -0.5, _stream()), l)

@@ -63,7 +63,7 @@ class SigmoidGate(Gate):
     @classmethod
     def wanted(cls, params):
         h = params["hidden_size"]
-        return {"weight": TensorWant((h, h)), "bias": TensorWant((h,))}
+        return {"weight": TensorWant((h, h)), "bias": TensorWant((h,), std_scale=10.0)}
 
     def __init__(self, params, load, rt):
         super().__init__(params, load, rt)

@@ -7,8 +7,10 @@
     S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q       float32; the read-out sees this token's write
     y = Wo( o / rms(o over value_dim) * w * silu(Wg x) )
 
-q and k have `n_kv_heads` heads; head h of v reads q/k head h // (n_heads // n_kv_heads).  The six projections
-that read x are one packed product.  A slot's state row holds the matrices of all heads and, behind them, the
+q and k have `n_kv_heads` heads; head h of v reads q/k head h // (n_heads // n_kv_heads).  The projections of q,
+k, v and the output gate are one packed product; those of beta and of the decay (two rows per head) are a
+second one whose result stays float32, because the decay's logit is multiplied by exp(A_h) and passes two
+exponentials, which would magnify a 16-bit rounding.  A slot's state row holds the matrices of all heads and, behind them, the
 last conv_taps - 1 inputs of the convolutions.  Upstream has no recurrent mixer.
 """
 from __future__ import annotations
@@ -33,8 +35,8 @@ class GatedDeltaRule(Mixer):
         taps = lambda rows: TensorWant((rows, K), std_scale=8.0)
         return {"q": TensorWant((Hk * d, hid)), "k": TensorWant((Hk * d, hid)), "v": TensorWant((H * dv, hid)),
                 "q.conv": taps(Hk * d), "k.conv": taps(Hk * d), "v.conv": taps(H * dv),
-                "b": TensorWant((H, hid)), "a": TensorWant((H, hid)), "A_log": TensorWant((H,)),
-                "dt_bias": TensorWant((H,)), "g": TensorWant((H * dv, hid)), "o": TensorWant((hid, H * dv)),
+                "b": TensorWant((H, hid)), "a": TensorWant((H, hid)), "A_log": TensorWant((H,), std_scale=10.0),
+                "dt_bias": TensorWant((H,), std_scale=10.0), "g": TensorWant((H * dv, hid)), "o": TensorWant((hid, H * dv)),
                 "norm": TensorWant((dv,), "norm")}
 
     def __init__(self, params, load, rt):
@@ -45,8 +47,9 @@ class GatedDeltaRule(Mixer):
         if self.H % self.Hk:
             raise ValueError(f"{self.H} heads are no multiple of {self.Hk} key heads")
         self.w_in, offs = pack_rows(load, (("q", self.Hk * self.d), ("k", self.Hk * self.d), ("v", self.H * self.dv),
-                                            ("g", self.H * self.dv), ("b", self.H), ("a", self.H)), self.hidden, rt)
-        self.q_off, self.k_off, self.v_off, self.g_off, self.b_off, self.a_off = offs
+                                            ("g", self.H * self.dv)), self.hidden, rt)
+        self.q_off, self.k_off, self.v_off, self.g_off = offs
+        self.w_ba, (self.b_off, self.a_off) = pack_rows(load, (("b", self.H), ("a", self.H)), self.hidden, rt)
         self.C = 2 * self.Hk * self.d + self.H * self.dv              # channels that pass the convolution
         self.taps = torch.cat([load("q.conv"), load("k.conv"), load("v.conv")]).contiguous()
         self.A_log, self.dt_bias = load("A_log"), load("dt_bias")
@@ -68,7 +71,8 @@ class GatedDeltaRule(Mixer):
         conv_state = cache.state[:, self.scan_floats:]
         qkv = kernels.causal_conv_silu(conv_in, self.taps, conv_state, ctx.tok_slot)
         kernels.conv_state_update(conv_in, self.K, conv_state, ctx.tok_slot)
-        o = kernels.delta_scan(qkv, (self.q_off, self.k_off, self.v_off), proj, (self.b_off, self.a_off), self.A_log,
+        ba = linear(x, self.w_ba, out_dtype=torch.float32)
+        o = kernels.delta_scan(qkv, (self.q_off, self.k_off, self.v_off), ba, (self.b_off, self.a_off), self.A_log,
                                self.dt_bias, cache.state, ctx.seq_spans(), ctx.tok_slot, self.H, self.Hk, self.d,
                                self.dv, self.unit_eps)
         y = kernels.gated_group_rmsnorm(o, proj[:, self.g_off:self.g_off + self.H * self.dv], self.norm, self.eps,

@@ -36,7 +36,7 @@ class LatentAttention(Mixer):
         w = {"q": TensorWant((H * (d + dr), hid)), "dkv": TensorWant((r + dr, hid)), "dkv.norm": TensorWant((r,), "norm"),
              "uk": TensorWant((H * d, r)), "uv": TensorWant((H * dv, r)), "o": TensorWant((hid, H * dv))}
         if params.get("sink", False):
-            w["sink"] = TensorWant((H,))
+            w["sink"] = TensorWant((H,), std_scale=20.0)
         return w
 
     def __init__(self, params, load, rt):

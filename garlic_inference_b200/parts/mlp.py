@@ -49,7 +49,7 @@ class XieluMLP(FeedForward):
     @classmethod
     def wanted(cls, params):
         h, i = params["hidden_size"], params["intermediate_size"]
-        return {"up": TensorWant((i, h)), "down": TensorWant((h, i)), "act": TensorWant((2,))}
+        return {"up": TensorWant((i, h)), "down": TensorWant((h, i)), "act": TensorWant((2,), std_scale=10.0)}
 
     def __init__(self, params, load, rt):
         super().__init__(params, load, rt)
