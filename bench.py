@@ -369,6 +369,181 @@ def study_prefill_clocks(model, prompt, gpu_id, flops) -> int:
     return 0
 
 
+# ---- the Fivitar design beside Qwen3 at equal layer sizes ------------------------------------------
+def fivitar_config_dict(width, heads, ff, vocab, n_layers, head_dim=128, kv_rank=512, rot_dim=64):
+    """`n_layers` layers that cycle through the three mixers, every one with a feed-forward, at sizes of a real
+    model's layers: heads of `head_dim` keys and values, a latent of `kv_rank` with a rotated part of `rot_dim`."""
+    def layer(i):
+        kind = ("delta", "lightning", "latent_attention")[i % 3]
+        if kind == "delta":
+            mixer = {"heads": heads, "kv_heads": max(1, heads // 2), "dim": head_dim, "vdim": head_dim, "conv": 4}
+        elif kind == "lightning":
+            mixer = {"heads": heads, "dim": head_dim, "vdim": head_dim,
+                     "decay": [1.0 - 2.0 ** (-5 - 3 * h / max(1, heads - 1)) for h in range(heads)]}
+        else:
+            mixer = {"heads": heads, "dim": head_dim, "rot_dim": rot_dim, "vdim": head_dim, "kv_rank": kv_rank,
+                     "scale": (head_dim + rot_dim) ** -0.5,
+                     "rot": {"base": 10000.0, "dims": rot_dim,
+                             "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+        return {"type": kind, "mixer": mixer, "mlp": {"kind": "dense", "ff": ff}}
+    return {"architecture": "Fivitar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "layers": [layer(i) for i in range(n_layers)]}
+
+
+def study_fivitar(args, pk) -> int:
+    """Prefill (one prompt of 2,048 tokens) and decode (batches of 1, 8 and 64 with 2,048 cached tokens each)
+    of Fivitar models with random weights, beside Qwen3 models of the same width, depth, heads and feed-forward
+    parameters, and every kernel of both timed alone at those sizes.  One JSON line."""
+    import torch
+    from garlic_inference_b200 import LanguageModel, Qwen3Config
+    from garlic_inference_b200.config import FivitarConfig
+    from garlic_inference_b200.ops import counters, kernels
+    from garlic_inference_b200.sampling import SamplingParams
+    K, W = min(args.steps, 64), max(min(args.warmup, 8), 3)
+    torch.cuda.set_device(0)
+    greedy = SamplingParams()
+    gen = torch.Generator().manual_seed(0)
+    sizes = [("1b", 2048, 16, 8192, 32000, 6), ("8b", 4096, 32, 18432, 32000, 6)]
+    out = {"study": "fivitar", "dtype": "bfloat16", "data": "synthetic", "steps": K, "warmup": W,
+           "peaks": pk, "models": {}, "kernels": {}}
+
+    def timed(fn, reps=5, warm=3):
+        for _ in range(warm):
+            fn()
+        flush = torch.empty(160 << 20, dtype=torch.uint8, device="cuda")
+        ms = []
+        for _ in range(reps):
+            flush.zero_()                                  # larger than L2: the next run starts cold
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record()
+            torch.cuda.synchronize()
+            ms.append(a.elapsed_time(b))
+        return statistics.median(ms)
+
+    def run_model(cfg, vocab):
+        per_seq = -(-(CACHED + W + K + 8) // 64) * 64
+        model = LanguageModel.from_random(cfg, seed=0, device=0, dtype="bfloat16", max_tokens=64 * per_seq,
+                                          max_slots=64)
+        eng, sampler = model.engine, model.sampler
+        prompt = lambda n: torch.randint(0, vocab, (n,), generator=gen).tolist()
+        res = {"weight_bytes": model.model.weight_bytes()}
+
+        def prefill_once():
+            s = eng.alloc_slot()
+            model.step([(s, prompt(PREFILL_TOKENS), [PREFILL_TOKENS - 1])])
+            eng.free_slot(s)
+        ms = timed(prefill_once, reps=5, warm=3)
+        res["prefill"] = {"tokens": PREFILL_TOKENS, "ms": round(ms, 3), "tokens_per_s": round(PREFILL_TOKENS / ms * 1e3)}
+        for batch in (1, 8, 64):
+            slots, firsts = [], []
+            for _ in range(batch):
+                s = eng.alloc_slot()
+                firsts.append(sampler.sample(model.step([(s, prompt(CACHED), [CACHED - 1])]), greedy, [0], [0]))
+                slots.append(s)
+            toks = torch.cat(firsts)
+            for _ in range(W):
+                toks = sampler.sample(eng.step_decode_device(slots, toks), greedy, slots, slots)
+            torch.cuda.synchronize()
+            n0 = counters.launches
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(K):
+                toks = sampler.sample(eng.step_decode_device(slots, toks), greedy, slots, slots)
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / K
+            state = eng.cache.state_bytes_per_slot * batch + eng.cache.bytes_per_token() * batch * CACHED
+            res[f"decode_b{batch}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(batch / ms * 1e3),
+                                       "launches_per_step": (counters.launches - n0) // K,
+                                       "bytes_read": res["weight_bytes"] + state,
+                                       "of_measured_copy": round((res["weight_bytes"] + state) / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 3)}
+            for s in slots:
+                eng.free_slot(s)
+        eng.check()
+        del model
+        torch.cuda.empty_cache()
+        return res
+
+    for label, width, heads, ff, vocab, n_layers in sizes:
+        fcfg = FivitarConfig.from_dict(fivitar_config_dict(width, heads, ff, vocab, n_layers))
+        inter = -(-(2 * ff // 3) // 256) * 256                      # three matrices instead of two: equal parameters
+        qcfg = Qwen3Config(hidden_size=width, num_hidden_layers=n_layers, num_attention_heads=heads,
+                           num_key_value_heads=max(1, heads // 4), head_dim=128, intermediate_size=inter,
+                           vocab_size=vocab, max_position_embeddings=CONTEXT * 2)
+        out["models"][label] = {"width": width, "heads": heads, "ff": ff, "layers": n_layers,
+                                "fivitar": run_model(fcfg, vocab), "qwen3": run_model(qcfg, vocab)}
+
+    # ---- the mixers' kernels alone, at the larger size: one prompt of 2,048 tokens, and 8 single tokens ----
+    H, d, dv, rank, dr, T, page = 32, 128, 128, 512, 64, PREFILL_TOKENS, 64
+    dev = "cuda"
+    bf = lambda *shape: torch.randn(*shape, device=dev, dtype=torch.bfloat16) * 0.5
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    from garlic_inference_b200.parts.linear_attention import scan_state_floats
+    sf = H * scan_state_floats(d, dv)
+    C = 2 * (H // 2) * d + H * dv
+    kern = out["kernels"]
+
+    def note(name, ms, flops=0.0, bytes_=0.0):
+        kern[name] = {"ms": round(ms, 4)}
+        if flops:
+            kern[name]["tflops"] = round(flops / ms / 1e9, 2)
+        if bytes_:
+            kern[name]["gbs"] = round(bytes_ / ms / 1e6, 1)
+            kern[name]["of_measured_copy"] = round(bytes_ / ms / 1e6 / pk["hbm_gbs"], 3)
+
+    for n_rows, tag, spans, slots in ((T, "prefill2048", i32([[0, 0, T]]), i32([0] * T)),
+                                      (8, "decode_b8", None, i32(list(range(8))))):
+        state = torch.zeros(9, sf + 3 * C + 8, device=dev)
+        qkvg = bf(n_rows, 4 * H * d)
+        decay = torch.full((H,), 0.99, device=dev)
+        ms = timed(lambda: kernels.decay_scan(qkvg, (0, H * d, 2 * H * d), decay, state[:, :sf], spans, slots, H, d, dv))
+        seqs = 1 if spans is not None else 8
+        note(f"decay_scan_{tag}", ms, flops=4.0 * n_rows * H * d * dv,
+             bytes_=seqs * 2 * sf * 4 + n_rows * (3 * H * d * 2 + H * dv * 4))
+        conv_out = torch.randn(n_rows, C, device=dev)
+        ba = torch.randn(n_rows, 2 * H, device=dev)
+        A, dtb = torch.zeros(H, device=dev), torch.zeros(H, device=dev)
+        ms = timed(lambda: kernels.delta_scan(conv_out, (0, H // 2 * d, H * d), ba, (0, H), A, dtb, state[:, :sf], spans,
+                                              slots, H, H // 2, d, dv, 1e-6))
+        note(f"delta_scan_{tag}", ms, flops=8.0 * n_rows * H * d * dv,
+             bytes_=seqs * 2 * sf * 4 + n_rows * (C * 4 + H * dv * 4))
+        x = bf(n_rows, C)
+        taps = bf(C, 4)
+        ms = timed(lambda: (kernels.causal_conv_silu(x, taps, state[:, sf:], slots),
+                            kernels.conv_state_update(x, 4, state[:, sf:], slots)))
+        note(f"conv_silu_and_state_{tag}", ms, bytes_=n_rows * C * (2 + 4))
+    # attention: the latent rows of one sequence of 2,048 (prefill) and of 8 sequences of 2,048 (decode)
+    row = rank + dr
+    pool = bf(8 * T // page, 1, page, row)
+    table = torch.arange(8 * T // page, dtype=torch.int32, device=dev).view(8, T // page)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    sinks = torch.zeros(H, device=dev)
+    q = bf(T, H, row)
+    pos, slot0 = torch.arange(T, dtype=torch.int32, device=dev), i32([0] * T)
+    ms = timed(lambda: kernels.attention_generic(q, pool, pool, table, pos, slot0, 0.07, 0, status, sinks=sinks,
+                                                 value_dim=rank), reps=3, warm=1)
+    note("latent_attention_prefill2048", ms, flops=2.0 * H * (row + rank) * T * (T + 1) / 2)
+    q8, pos8 = bf(8, H, row), i32([T - 1] * 8)
+    ms = timed(lambda: kernels.attention_generic(q8, pool, pool, table, pos8, i32(list(range(8))), 0.07, 0, status,
+                                                 sinks=sinks, value_dim=rank))
+    note("latent_attention_decode_b8", ms, bytes_=8 * T * row * 2)
+    # the closest existing kernels: grouped-query flash attention over 2,048 tokens, and split-KV decoding
+    from garlic_inference_b200.parts.attention import query_runs
+    from garlic_inference_b200.parts import StepShape
+    n_kv = 8
+    kp, vp = bf(8 * T // page, n_kv, page, 128), bf(8 * T // page, n_kv, page, 128)
+    qq = bf(T, H, 128)
+    runs = torch.from_numpy(query_runs(StepShape([0], [0], [T], [0], False), 128)).to(dev)
+    ms = timed(lambda: kernels.attention_prefill_tcgen05(qq, kp, vp, table, runs, 0.088, 0, rows_covered=True))
+    note("gqa_attention_prefill2048_tcgen05", ms, flops=4.0 * H * 128 * T * (T + 1) / 2)
+    qd, slots8 = bf(8, H, 128), i32(list(range(8)))
+    ms = timed(lambda: kernels.attention_decode_tcgen05(qd, kp, vp, table, pos8, slots8, 0.088, 0))
+    note("gqa_attention_decode_b8_tcgen05", ms, bytes_=8 * T * 2 * n_kv * 128 * 2)
+    kernels.check_bounded_waits(torch.device("cuda", 0))
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -382,9 +557,11 @@ def main() -> int:
     ap.add_argument("--write-model", default=None, metavar="DIR",
                     help="with --impl reference: only write the model folder that arm uses (tied head, --layers of the 36) "
                          "to DIR and exit, for running baseline/_ref/bin/reference_runner by hand or under a profiler")
-    ap.add_argument("--study", default=None, choices=["prefill-clocks"],
+    ap.add_argument("--study", default=None, choices=["prefill-clocks", "fivitar"],
                     help="prefill-clocks: 40 prompt steps of 2,048 tokens back to back with the clock and the power "
-                         "sampled every 20 ms; prints a table and no JSON line")
+                         "sampled every 20 ms; prints a table and no JSON line.  fivitar: prefill and decode of the "
+                         "Fivitar design at two sizes of real layers beside Qwen3 at equal sizes, and the mixers' "
+                         "kernels alone; one JSON line of its own")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -399,6 +576,9 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported (nothing was run)")
         return 2
+
+    if args.study == "fivitar":
+        return study_fivitar(args, peaks())
 
     import torch
     from garlic_inference_b200 import LanguageModel, Qwen3Config

@@ -1,5 +1,5 @@
 // Attention over the paged cache for any number of new tokens per sequence,
-// float32 or bfloat16, any head_dim that is a multiple of 8 up to 512.
+// float32 or bfloat16, any head_dim that is a multiple of 8 up to 1024.
 //
 // This is the engine's exact path: the float32 engine uses it for prompts and
 // for decoding alike, and the bfloat16 engine uses it for head sizes its
@@ -155,7 +155,8 @@ static int launch_generic(const void* q, const void* k_pool, const void* v_pool,
     else if (d <= 64) AG_LAUNCH(2);
     else if (d <= 128) AG_LAUNCH(4);
     else if (d <= 256) AG_LAUNCH(8);
-    else AG_LAUNCH(16);
+    else if (d <= 512) AG_LAUNCH(16);
+    else AG_LAUNCH(32);
 #undef AG_LAUNCH
     return gi_check_launch("gi_attention_generic");
 }
@@ -167,7 +168,7 @@ extern "C" int gi_attention_generic(const void* q, const void* k_pool, const voi
                                     int sink_dtype, int d_v, int* status, void* stream) {
     GI_REQUIRE(n_tokens >= 0 && n_q > 0 && n_kv > 0 && d > 0, "gi_attention_generic: sizes must be positive");
     GI_REQUIRE(n_q % n_kv == 0, "gi_attention_generic: %d query heads are no multiple of %d key/value heads", n_q, n_kv);
-    GI_REQUIRE(d % 8 == 0 && d <= 512, "gi_attention_generic: head_dim %d must be a multiple of 8, at most 512", d);
+    GI_REQUIRE(d % 8 == 0 && d <= 1024, "gi_attention_generic: head_dim %d must be a multiple of 8, at most 1024", d);
     GI_REQUIRE(n_q <= 65535, "gi_attention_generic: %d query heads is beyond 65535", n_q);
     GI_REQUIRE(d_v > 0 && d_v <= d, "gi_attention_generic: %d value columns of rows of %d", d_v, d);
     GI_REQUIRE(page_size > 0 && max_pages > 0 && window >= 0, "gi_attention_generic: page size, table width and window");
