@@ -342,6 +342,23 @@ def delta_scan(qkv: torch.Tensor, offsets: tuple, ab: torch.Tensor, ab_offsets: 
     return out
 
 
+def causal_sink_softmax(scores: torch.Tensor, heads: int, first_pos: int, scale: float,
+                        sinks: Optional[torch.Tensor], out_dtype: torch.dtype) -> torch.Tensor:
+    """Softmax over the rows of float32 `scores` [tokens * heads, keys]: row t * heads + h belongs to the query at
+    position first_pos + t and sees keys 0 .. first_pos + t; `scale` multiplies the scores; exp(sinks[h]) joins the
+    denominator.  Returns the weights [tokens * heads, keys] in `out_dtype`, zeros beyond each row's position."""
+    l = require_gpu()
+    _rows(scores, "scores", torch.float32)
+    n, keys = scores.shape
+    if sinks is not None and _dense(sinks, "sinks").numel() != heads:
+        raise KernelError(f"{sinks.numel()} sinks for {heads} heads")
+    out = torch.empty((n, keys), dtype=out_dtype, device=scores.device)
+    check(l.gi_causal_sink_softmax(_ptr(scores), scores.stride(0), _ptr(out), keys, code(out_dtype), n, heads,
+                                   int(first_pos), keys, float(scale), _ptr(sinks),
+                                   code(sinks.dtype) if sinks is not None else F32, _stream()), l)
+    return out
+
+
 def latent_prepare(proj: torch.Tensor, q_off: int, c_off: int, q_lat: torch.Tensor, norm_w: torch.Tensor, eps: float,
                    freq: torch.Tensor, magnitude: float, n_rot: int, tok_pos: torch.Tensor, tok_slot: torch.Tensor,
                    block_table: torch.Tensor, pool: torch.Tensor, n_heads: int, plain_dim: int, rot_dim: int,

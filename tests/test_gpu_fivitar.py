@@ -249,3 +249,21 @@ def test_attention_sinks_and_narrow_values():
     want = torch.einsum("htj,jv->thv", p, rows[:, :dv]).reshape(T, H * dv)
     torch.testing.assert_close(got.cpu(), want, rtol=1e-5, atol=1e-5)
     assert int(status.item()) == 0
+
+
+def test_causal_sink_softmax_kernel():
+    from garlic_inference_b200.ops import kernels
+    torch.manual_seed(3)
+    H, T, first, keys = 3, 5, 9, 16
+    wide = torch.randn(T * H, keys + 5, device="cuda") * 4
+    scores = wide[:, :keys]
+    sinks = torch.tensor([0.2, -3.0, 2.5], device="cuda")
+    for sk in (sinks, None):
+        got = kernels.causal_sink_softmax(scores, H, first, 0.7, sk, torch.float32).cpu().view(T, H, keys)
+        s = scores.cpu().view(T, H, keys) * 0.7
+        seen = torch.arange(keys)[None, None, :] <= (first + torch.arange(T))[:, None, None]
+        e = torch.where(seen, torch.exp(s), torch.zeros(()))
+        extra = torch.exp(sinks.cpu())[None, :, None] if sk is not None else 0.0
+        torch.testing.assert_close(got, e / (e.sum(-1, keepdim=True) + extra), rtol=1e-5, atol=1e-7)
+    got = kernels.causal_sink_softmax(scores, H, first, 0.7, sinks, torch.bfloat16)
+    assert got.dtype == torch.bfloat16 and float(got.view(T, H, keys)[0, :, first + 1:].abs().max()) == 0.0
