@@ -522,11 +522,22 @@ def study_fivitar(args, pk) -> int:
     pos, slot0 = torch.arange(T, dtype=torch.int32, device=dev), i32([0] * T)
     ms = timed(lambda: kernels.attention_generic(q, pool, pool, table, pos, slot0, 0.07, 0, status, sinks=sinks,
                                                  value_dim=rank), reps=3, warm=1)
-    note("latent_attention_prefill2048", ms, flops=2.0 * H * (row + rank) * T * (T + 1) / 2)
-    q8, pos8 = bf(8, H, row), i32([T - 1] * 8)
-    ms = timed(lambda: kernels.attention_generic(q8, pool, pool, table, pos8, i32(list(range(8))), 0.07, 0, status,
+    note("latent_attention_prefill2048_exact_order", ms, flops=2.0 * H * (row + rank) * T * (T + 1) / 2)
+    rows = pool.view(-1, page, row)[:T // page].reshape(T, row)
+
+    def by_products():                       # what the mixer runs for a prompt in bfloat16: blocks of 1,024 tokens
+        for q0 in range(0, T, 1024):
+            scores = torch.mm(q[q0:q0 + 1024].view(1024 * H, row), rows[:q0 + 1024].t(), out_dtype=torch.float32)
+            w = kernels.causal_sink_softmax(scores, H, q0, 0.07, sinks, torch.bfloat16)
+            torch.mm(w, rows[:q0 + 1024, :rank])
+    ms = timed(by_products)
+    note("latent_attention_prefill2048_products", ms, flops=2.0 * H * (row + rank) * T * (T + 1) / 2)
+    q8, pos8, slots8 = bf(8, H, row), i32([T - 1] * 8), i32(list(range(8)))
+    ms = timed(lambda: kernels.attention_generic(q8, pool, pool, table, pos8, slots8, 0.07, 0, status,
                                                  sinks=sinks, value_dim=rank))
-    note("latent_attention_decode_b8", ms, bytes_=8 * T * row * 2)
+    note("latent_attention_decode_b8_exact_order", ms, bytes_=8 * T * row * 2)
+    ms = timed(lambda: kernels.latent_decode(q8, pool, table, pos8, slots8, 0.07, sinks, rank, status))
+    note("latent_attention_decode_b8_shared_rows", ms, flops=2.0 * 8 * H * (row + rank) * T, bytes_=8 * T * row * 2)
     # the closest existing kernels: grouped-query flash attention over 2,048 tokens, and split-KV decoding
     from garlic_inference_b200.parts.attention import query_runs
     from garlic_inference_b200.parts import StepShape
@@ -536,7 +547,7 @@ def study_fivitar(args, pk) -> int:
     runs = torch.from_numpy(query_runs(StepShape([0], [0], [T], [0], False), 128)).to(dev)
     ms = timed(lambda: kernels.attention_prefill_tcgen05(qq, kp, vp, table, runs, 0.088, 0, rows_covered=True))
     note("gqa_attention_prefill2048_tcgen05", ms, flops=4.0 * H * 128 * T * (T + 1) / 2)
-    qd, slots8 = bf(8, H, 128), i32(list(range(8)))
+    qd = bf(8, H, 128)
     ms = timed(lambda: kernels.attention_decode_tcgen05(qd, kp, vp, table, pos8, slots8, 0.088, 0))
     note("gqa_attention_decode_b8_tcgen05", ms, bytes_=8 * T * 2 * n_kv * 128 * 2)
     kernels.check_bounded_waits(torch.device("cuda", 0))

@@ -109,3 +109,188 @@ extern "C" int gi_latent_prepare(const void* proj, long long ld, int q_off, int 
         GI_REQUIRE(false, "gi_latent_prepare: activation dtype %d", act_dtype);
     return gi_check_launch("gi_latent_prepare");
 }
+
+// ------------------------------------------------------------------ attention of single tokens over the latent rows
+// Decode steps in bfloat16: one new token per sequence, all heads of a sequence read the same cached rows.  A
+// block takes one token, up to 8 * HPW heads and one slice of the keys; it stages 32 rows at a time in shared
+// memory, where every head's scores and weighted sums read them (the exact-order kernel fetches them once per
+// head).  Warp w owns heads w HPW .. w HPW + HPW - 1 of the block's group for all keys of the slice, so the
+// running maximum and sum stay inside the warp; lane j scores key j of the 32, then the lanes turn to pairs of
+// value columns.  Scores, softmax and sums are float32.  The slices' (max, sum, weighted rows) go to `part`
+// [tokens, slices, heads, 2 + rank] and gi_latent_decode_combine merges them with the sink.
+#define LD_WARPS 8
+#define LD_KEYS 32
+
+__device__ __forceinline__ float2 bf2_to_f2(uint32_t w) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
+}
+
+template <int HPW, int DPL2>
+__global__ void __launch_bounds__(LD_WARPS * 32)
+latent_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pool, const int* __restrict__ block_table,
+                     const int* __restrict__ tok_pos, const int* __restrict__ tok_slot, float* __restrict__ part,
+                     int H, int dk, int rank, int page_size, int max_pages, int n_pool_pages, int n_splits,
+                     float scale, int* __restrict__ status) {
+    gi_pdl_start();
+    extern __shared__ __align__(16) unsigned char ld_smem[];
+    constexpr int HG = HPW * LD_WARPS;
+    float* q_s = reinterpret_cast<float*>(ld_smem);                  // HG rows of dk
+    uint32_t* k_s = reinterpret_cast<uint32_t*>(q_s + HG * dk);      // 32 rows of kw words (kw odd: no bank conflicts)
+    const int kw = dk / 2 + 1;
+    const int t = blockIdx.x, split = blockIdx.y, h0 = blockIdx.z * HG;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int slot = tok_slot[t], pos = tok_pos[t];
+    const size_t stride = (size_t)rank + 2;
+    float* my = part + ((size_t)t * n_splits + split) * H * stride;
+    const bool dead = slot < 0 || pos < 0 || pos / page_size >= max_pages;
+    const int n_chunks = dead ? 0 : pos / LD_KEYS + 1;
+    const int per = (n_chunks + n_splits - 1) / n_splits;
+    const int c0 = split * per, c1 = min(n_chunks, c0 + per);
+    if (dead && slot >= 0 && threadIdx.x == 0) atomicExch(status, 4);
+
+    if (c0 < c1)
+        for (int i = threadIdx.x; i < HG * dk; i += blockDim.x) {
+            const int hh = i / dk, c = i - hh * dk;
+            q_s[i] = h0 + hh < H ? to_f32(q[((size_t)t * H + h0 + hh) * dk + c]) * scale : 0.f;
+        }
+    float m[HPW], l[HPW], p[HPW], acc[HPW][2 * DPL2];
+#pragma unroll
+    for (int hh = 0; hh < HPW; ++hh) {
+        m[hh] = -INFINITY; l[hh] = 0.f;
+#pragma unroll
+        for (int r = 0; r < 2 * DPL2; ++r) acc[hh][r] = 0.f;
+    }
+    const int* bt = block_table + (size_t)(dead ? 0 : slot) * max_pages;
+    const int vec_per_row = dk / 8;
+    for (int c = c0; c < c1; ++c) {
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < LD_KEYS * vec_per_row; idx += blockDim.x) {
+            const int j = idx / vec_per_row, v = idx - j * vec_per_row;
+            const int key = c * LD_KEYS + j;
+            uint4 val = make_uint4(0u, 0u, 0u, 0u);
+            if (key <= pos) {
+                const int page = bt[key / page_size];
+                if (page < 0 || page >= n_pool_pages) atomicExch(status, 5);
+                else val = *reinterpret_cast<const uint4*>(pool + ((size_t)page * page_size + key % page_size) * dk + v * 8);
+            }
+            uint32_t* dst = k_s + j * kw + v * 4;
+            dst[0] = val.x; dst[1] = val.y; dst[2] = val.z; dst[3] = val.w;
+        }
+        __syncthreads();
+        const bool valid = c * LD_KEYS + lane <= pos;
+        float s[HPW];
+#pragma unroll
+        for (int hh = 0; hh < HPW; ++hh) s[hh] = 0.f;
+        const uint32_t* kr = k_s + lane * kw;
+        const float* qw = q_s + (size_t)warp * HPW * dk;
+        for (int i2 = 0; i2 < dk / 2; ++i2) {
+            const float2 kf = bf2_to_f2(kr[i2]);
+#pragma unroll
+            for (int hh = 0; hh < HPW; ++hh) {
+                const float2 qf = *reinterpret_cast<const float2*>(qw + hh * dk + 2 * i2);
+                s[hh] = fmaf(kf.x, qf.x, s[hh]);
+                s[hh] = fmaf(kf.y, qf.y, s[hh]);
+            }
+        }
+#pragma unroll
+        for (int hh = 0; hh < HPW; ++hh) {
+            const float sv = valid ? s[hh] : -INFINITY;
+            const float m_new = fmaxf(m[hh], warp_max(sv));          // the chunk's first key is always seen
+            const float corr = expf(m[hh] - m_new);
+            p[hh] = valid ? expf(sv - m_new) : 0.f;
+            l[hh] = l[hh] * corr + warp_sum(p[hh]);
+            m[hh] = m_new;
+#pragma unroll
+            for (int r = 0; r < 2 * DPL2; ++r) acc[hh][r] *= corr;
+        }
+        for (int j = 0; j < LD_KEYS; ++j) {
+            float pj[HPW];
+#pragma unroll
+            for (int hh = 0; hh < HPW; ++hh) pj[hh] = __shfl_sync(0xffffffffu, p[hh], j);
+#pragma unroll
+            for (int r = 0; r < DPL2; ++r) {
+                const int col2 = lane + 32 * r;
+                if (2 * col2 < rank) {
+                    const float2 vf = bf2_to_f2(k_s[j * kw + col2]);
+#pragma unroll
+                    for (int hh = 0; hh < HPW; ++hh) {
+                        acc[hh][2 * r] = fmaf(pj[hh], vf.x, acc[hh][2 * r]);
+                        acc[hh][2 * r + 1] = fmaf(pj[hh], vf.y, acc[hh][2 * r + 1]);
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int hh = 0; hh < HPW; ++hh) {
+        const int h = h0 + warp * HPW + hh;
+        if (h >= H) continue;
+        float* o = my + (size_t)h * stride;
+        if (lane == 0) { o[0] = m[hh]; o[1] = l[hh]; }
+#pragma unroll
+        for (int r = 0; r < DPL2; ++r) {
+            const int col = 2 * (lane + 32 * r);
+            if (col < rank) o[2 + col] = acc[hh][2 * r];
+            if (col + 1 < rank) o[2 + col + 1] = acc[hh][2 * r + 1];
+        }
+    }
+}
+
+__global__ void latent_decode_combine_kernel(const float* __restrict__ part, bf16* __restrict__ out, int H, int rank,
+                                             int n_splits, const void* __restrict__ sinks, int sink_dtype) {
+    gi_pdl_start();
+    const int t = blockIdx.x, h = blockIdx.y;
+    const size_t stride = (size_t)rank + 2;
+    const float* base = part + ((size_t)t * n_splits * H + h) * stride;
+    const size_t step = (size_t)H * stride;
+    const float sink = sinks ? load_w(sinks, sink_dtype, h) : -INFINITY;
+    float M = sink;
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, base[s * step]);
+    float L = sinks ? expf(sink - M) : 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float ms = base[s * step];
+        if (ms != -INFINITY) L += expf(ms - M) * base[s * step + 1];
+    }
+    for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+        float v = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = base[s * step];
+            if (ms != -INFINITY) v += expf(ms - M) * base[s * step + 2 + c];
+        }
+        out[((size_t)t * H + h) * rank + c] = __float2bfloat16_rn(L > 0.f ? v / L : 0.f);
+    }
+}
+
+extern "C" int gi_latent_decode(const void* q, const void* pool, const int* block_table, const int* tok_pos,
+                                const int* tok_slot, float* part, void* out, int n_tokens, int H, int dk, int rank,
+                                int page_size, int max_pages, int n_pool_pages, int n_splits, float scale,
+                                const void* sinks, int sink_dtype, int* status, void* stream) {
+    GI_REQUIRE(n_tokens >= 0 && H > 0 && dk > 0 && dk % 8 == 0 && rank > 0 && rank <= dk && rank <= 512,
+               "gi_latent_decode: rows of %d (a multiple of 8) with %d value columns (at most 512)", dk, rank);
+    GI_REQUIRE(n_splits >= 1 && n_splits <= 64 && H <= 65535 && n_tokens <= 65535, "gi_latent_decode: slices, heads, tokens");
+    if (n_tokens == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int HPW = H > 16 ? 4 : (H > 8 ? 2 : 1);
+    const int HG = HPW * LD_WARPS;
+    const int DPL2 = rank > 256 ? 8 : (rank > 128 ? 4 : (rank > 64 ? 2 : 1));
+    const size_t smem = (size_t)HG * dk * 4 + (size_t)LD_KEYS * (dk / 2 + 1) * 4;
+    GI_REQUIRE(smem <= 220 * 1024, "gi_latent_decode: rows of %d need %zu bytes of shared memory", dk, smem);
+    dim3 grid(n_tokens, n_splits, (H + HG - 1) / HG);
+#define LD_CASE(A, B)                                                                                             \
+    if (HPW == A && DPL2 == B) {                                                                                  \
+        int rc = gi_reserve_smem((const void*)latent_decode_kernel<A, B>, smem, "gi_latent_decode");              \
+        if (rc) return rc;                                                                                        \
+        gi_launch(latent_decode_kernel<A, B>, grid, dim3(LD_WARPS * 32), smem, s, (const bf16*)q, (const bf16*)pool, \
+                  block_table, tok_pos, tok_slot, part, H, dk, rank, page_size, max_pages, n_pool_pages, n_splits, \
+                  scale, status);                                                                                 \
+    }
+    LD_CASE(1, 1) LD_CASE(1, 2) LD_CASE(1, 4) LD_CASE(1, 8)
+    LD_CASE(2, 1) LD_CASE(2, 2) LD_CASE(2, 4) LD_CASE(2, 8)
+    LD_CASE(4, 1) LD_CASE(4, 2) LD_CASE(4, 4) LD_CASE(4, 8)
+#undef LD_CASE
+    int rc = gi_check_launch("gi_latent_decode");
+    if (rc) return rc;
+    gi_launch(latent_decode_combine_kernel, dim3(n_tokens, H), dim3(128), 0, s, (const float*)part, (bf16*)out, H, rank,
+              n_splits, sinks, sink_dtype);
+    return gi_check_launch("gi_latent_decode_combine");
+}

@@ -359,6 +359,40 @@ def causal_sink_softmax(scores: torch.Tensor, heads: int, first_pos: int, scale:
     return out
 
 
+def latent_decode_takes(dtype: torch.dtype, row: int, rank: int, heads: int) -> bool:
+    """Whether the shared-rows decode kernel takes these sizes (bfloat16, rows a multiple of 8, at most 512 value
+    columns, and shared memory for a group of heads beside 32 rows)."""
+    group = 8 * (4 if heads > 16 else (2 if heads > 8 else 1))
+    return (dtype == torch.bfloat16 and row % 8 == 0 and 0 < rank <= min(row, 512)
+            and group * row * 4 + 32 * (row // 2 + 1) * 4 <= 220 * 1024)
+
+
+def latent_decode(q: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor, tok_pos: torch.Tensor,
+                  tok_slot: torch.Tensor, scale: float, sinks: Optional[torch.Tensor], rank: int,
+                  status: torch.Tensor, n_splits: Optional[int] = None) -> torch.Tensor:
+    """Attention of one new token per sequence, q [n, heads, row] bfloat16, over latent rows shared by all heads
+    (`pool` [pages, 1, page_size, row]); values are the rows' first `rank` columns.  Returns [n, heads * rank]."""
+    l = require_gpu()
+    _dense(q, "q", torch.bfloat16), _dense(pool, "pool", torch.bfloat16)
+    for t, name in ((tok_pos, "tok_pos"), (tok_slot, "tok_slot"), (block_table, "block_table"), (status, "status")):
+        _dense(t, name, torch.int32)
+    n, heads, row = q.shape
+    n_pages, one, page_size, pool_row = pool.shape
+    if one != 1 or pool_row != row:
+        raise KernelError(f"a pool {tuple(pool.shape)} does not hold rows of {row} shared by all heads")
+    if n_splits is None:                       # enough blocks for two per SM, no slice shorter than 64 keys' worth
+        groups = -(-heads // (8 * (4 if heads > 16 else (2 if heads > 8 else 1))))
+        n_splits = max(1, min(32, -(-296 // max(1, n * groups))))
+    part = torch.empty((n, n_splits, heads, rank + 2), dtype=torch.float32, device=q.device)
+    out = torch.empty((n, heads * rank), dtype=torch.bfloat16, device=q.device)
+    check(l.gi_latent_decode(_ptr(q), _ptr(pool), _ptr(block_table), _ptr(tok_pos), _ptr(tok_slot), _ptr(part),
+                             _ptr(out), n, heads, row, rank, page_size, block_table.shape[1], n_pages, n_splits,
+                             float(scale), _ptr(sinks), code(sinks.dtype) if sinks is not None else F32,
+                             _ptr(status), _stream()), l)
+    counters.launches += 1                     # two kernels behind one entry point
+    return out
+
+
 def latent_prepare(proj: torch.Tensor, q_off: int, c_off: int, q_lat: torch.Tensor, norm_w: torch.Tensor, eps: float,
                    freq: torch.Tensor, magnitude: float, n_rot: int, tok_pos: torch.Tensor, tok_slot: torch.Tensor,
                    block_table: torch.Tensor, pool: torch.Tensor, n_heads: int, plain_dim: int, rot_dim: int,

@@ -40,6 +40,7 @@ _SIGNATURES = {
     "gi_decay_scan": ([P, L, I, I, I, I, P, P, L, P, P, P, I, I, I, I, P], I),
     "gi_delta_scan": ([P, L, I, I, I, P, L, I, I, P, P, I, P, L, P, P, P, I, I, I, I, I, F, F, P], I),
     "gi_causal_sink_softmax": ([P, L, P, L, I, I, I, I, I, F, P, I, P], I),
+    "gi_latent_decode": ([P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, I, P, P], I),
     "gi_latent_prepare": ([P, L, I, I, P, I, P, I, F, P, F, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, P], I),
     "gi_attention_prefill_bf16": ([P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, P], I),
     "gi_attention_prefill_tcgen05": ([P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, F, P, P], I),

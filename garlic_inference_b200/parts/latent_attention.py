@@ -11,8 +11,10 @@ Only c and rot(kr) are cached: one row per position in a single-plane paged entr
 materialised: q'_h = Wuk,h^T q_plain,h is made by a per-head product, attention runs over the cached rows for
 all heads (score q'_h . c_j + rot(q_rot) . rot(kr_j), values c_j), and Wuv,h is applied to the result.
 
-Which attention runs.  Single tokens, short portions and everything under float32: the exact-order kernel
-(scores, softmax and weighted sum float32, one block per token and head).  Portions of `PRODUCT_MIN_ROWS`
+Which attention runs.  Everything under float32, and short portions: the exact-order kernel (scores, softmax
+and weighted sum float32, one block per token and head).  Decode steps in bfloat16: the shared-rows kernel,
+which stages the cached rows in shared memory once for all heads and cuts the keys into slices (float32
+scores, softmax and sums as well).  Portions of `PRODUCT_MIN_ROWS`
 tokens and more in bfloat16: because all heads share the cached rows, the scores of a block of tokens are one
 matrix product [tokens x heads, row] . [row, keys] with float32 results, the softmax (causal, with the sink,
 float32) is this package's kernel, and the weighted sum is a second product [tokens x heads, keys] . [keys,
@@ -102,6 +104,9 @@ class LatentAttention(Mixer):
         """Attention of q_rows [n, H, row] over the cached rows; returns [n, H * kv_rank]."""
         by_products = (q_rows.dtype == torch.bfloat16 and not ctx.all_single and not ctx.captured and ctx.seq_lens
                        and max(ctx.seq_lens) >= PRODUCT_MIN_ROWS)
+        if ctx.all_single and kernels.latent_decode_takes(q_rows.dtype, q_rows.shape[2], self.rank, self.H):
+            return kernels.latent_decode(q_rows, kv.k_pool, kv.block_table, ctx.tok_pos, ctx.tok_slot, self.scale,
+                                         self.sink, self.rank, ctx.status)
         if not by_products:
             return kernels.attention_generic(q_rows, kv.k_pool, kv.k_pool, kv.block_table, ctx.tok_pos, ctx.tok_slot,
                                              self.scale, 0, ctx.status, sinks=self.sink, value_dim=self.rank)
