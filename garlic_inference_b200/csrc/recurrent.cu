@@ -96,7 +96,10 @@ extern "C" int gi_causal_conv_silu(const void* x, long long ldx, int act_dtype, 
 }
 
 // ------------------------------------------------------------------ scans
-#define SCAN_TC 8            // tokens staged in shared memory at a time
+// Tokens staged in shared memory at a time: 32 (16 for the widest keys, to stay inside 48 KB).  A chunk costs one
+// round trip to global memory that nothing hides when a block has its SM to itself (one long prompt), so the
+// chunk is as long as shared memory allows; the results do not depend on it.
+#define SCAN_TC(R) ((R) <= 32 ? 32 : 16)
 #define SCAN_VS 32           // value columns per block
 #define SCAN_THREADS 128
 
@@ -138,13 +141,15 @@ __global__ void __launch_bounds__(SCAN_THREADS)
 decay_scan_kernel(const T* __restrict__ qkv, long long ld, int q_off, int k_off, int v_off,
                   const float* __restrict__ decay, float* __restrict__ state, long long state_stride,
                   const int* __restrict__ spans, const int* __restrict__ tok_slot, float* __restrict__ out,
-                  int H, int d, int dv) {
+                  int H, int d, int dv, int vec_rows) {
     gi_pdl_start();
+    const bool vec = sizeof(T) == 2 && vec_rows;       // rows that can be fetched 16 bytes at a time
     constexpr int DP = 4 * R;                          // padded key dimension
-    __shared__ __align__(16) float q_s[SCAN_TC][DP];
-    __shared__ __align__(16) float k_s[SCAN_TC][DP];
-    __shared__ float v_s[SCAN_TC][SCAN_VS];
-    __shared__ float o_s[SCAN_TC][SCAN_VS];
+    constexpr int TC = SCAN_TC(R);
+    __shared__ __align__(16) float q_s[TC][DP];
+    __shared__ __align__(16) float k_s[TC][DP];
+    __shared__ float v_s[TC][SCAN_VS];
+    __shared__ float o_s[TC][SCAN_VS];
     int slot, start, len;
     scan_span(spans, tok_slot, blockIdx.x, slot, start, len);
     const int h = blockIdx.y, v0 = blockIdx.z * SCAN_VS;
@@ -164,20 +169,65 @@ decay_scan_kernel(const T* __restrict__ qkv, long long ld, int q_off, int k_off,
 #pragma unroll
         for (int e = 0; e < R; ++e) S[e] = 0.f;
     }
-    for (int t0 = 0; t0 < len; t0 += SCAN_TC) {
-        const int tc = min(SCAN_TC, len - t0);
-        __syncthreads();                               // the last chunk's o_s and inputs are done with
-        for (int i = threadIdx.x; i < tc * DP; i += SCAN_THREADS) {
-            const int t = i / DP, c = i - t * DP;
-            const T* row = qkv + (size_t)(start + t0 + t) * ld;
-            q_s[t][c] = c < d ? rc_silu(to_f32(row[q_off + h * d + c])) : 0.f;
-            k_s[t][c] = c < d ? rc_silu(to_f32(row[k_off + h * d + c])) : 0.f;
+    // Staging.  bfloat16 rows whose heads start on 16 bytes: every thread fetches NV vectors of 8 values of q and
+    // k (and one of v) into registers, all at once, and the next chunk's are fetched before this chunk's tokens
+    // are walked, so their latency hides behind the walk.  Otherwise: element by element.
+    constexpr int VPT = DP / 8;                        // vectors per token and operand
+    constexpr int NV = (TC * VPT * 2 + SCAN_THREADS - 1) / SCAN_THREADS;
+    uint4 pre[NV], pre_v;
+    auto fetch = [&](int t0) {
+        const int tc = min(TC, len - t0);
+#pragma unroll
+        for (int n = 0; n < NV; ++n) {
+            const int slot_i = threadIdx.x + SCAN_THREADS * n;
+            const int which = slot_i / (TC * VPT), rem = slot_i - which * (TC * VPT);
+            const int t = rem / VPT, vc = rem - t * VPT;
+            pre[n] = make_uint4(0u, 0u, 0u, 0u);
+            if (which < 2 && t < tc && vc * 8 < d)
+                pre[n] = *reinterpret_cast<const uint4*>(qkv + (size_t)(start + t0 + t) * ld + (which ? k_off : q_off) + h * d + vc * 8);
         }
-        for (int i = threadIdx.x; i < tc * SCAN_VS; i += SCAN_THREADS) {
-            const int t = i / SCAN_VS, c = i - t * SCAN_VS;
-            v_s[t][c] = v0 + c < dv ? rc_silu(to_f32(qkv[(size_t)(start + t0 + t) * ld + v_off + h * dv + v0 + c])) : 0.f;
+        const int t = threadIdx.x / (SCAN_VS / 8), vc = threadIdx.x - t * (SCAN_VS / 8);
+        pre_v = make_uint4(0u, 0u, 0u, 0u);
+        if (t < tc && v0 + vc * 8 < dv)
+            pre_v = *reinterpret_cast<const uint4*>(qkv + (size_t)(start + t0 + t) * ld + v_off + h * dv + v0 + vc * 8);
+    };
+    auto silu8 = [](const uint4& w, float* dst) {
+        const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&w);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(p2[i]);
+            dst[2 * i] = rc_silu(f.x);
+            dst[2 * i + 1] = rc_silu(f.y);
+        }
+    };
+    if (vec) fetch(0);
+    for (int t0 = 0; t0 < len; t0 += TC) {
+        const int tc = min(TC, len - t0);
+        __syncthreads();                               // the last chunk's o_s and inputs are done with
+        if (vec) {
+#pragma unroll
+            for (int n = 0; n < NV; ++n) {
+                const int slot_i = threadIdx.x + SCAN_THREADS * n;
+                const int which = slot_i / (TC * VPT), rem = slot_i - which * (TC * VPT);
+                const int t = rem / VPT, vc = rem - t * VPT;
+                if (which < 2 && t < tc) silu8(pre[n], (which ? &k_s[t][0] : &q_s[t][0]) + vc * 8);   // silu(0) = 0: the padding
+            }
+            const int t = threadIdx.x / (SCAN_VS / 8), vc = threadIdx.x - t * (SCAN_VS / 8);
+            if (t < tc) silu8(pre_v, &v_s[t][vc * 8]);
+        } else {
+            for (int i = threadIdx.x; i < tc * DP; i += SCAN_THREADS) {
+                const int t = i / DP, c = i - t * DP;
+                const T* row = qkv + (size_t)(start + t0 + t) * ld;
+                q_s[t][c] = c < d ? rc_silu(to_f32(row[q_off + h * d + c])) : 0.f;
+                k_s[t][c] = c < d ? rc_silu(to_f32(row[k_off + h * d + c])) : 0.f;
+            }
+            for (int i = threadIdx.x; i < tc * SCAN_VS; i += SCAN_THREADS) {
+                const int t = i / SCAN_VS, c = i - t * SCAN_VS;
+                v_s[t][c] = v0 + c < dv ? rc_silu(to_f32(qkv[(size_t)(start + t0 + t) * ld + v_off + h * dv + v0 + c])) : 0.f;
+            }
         }
         __syncthreads();
+        if (vec && t0 + TC < len) fetch(t0 + TC);
         for (int t = 0; t < tc; ++t) {
             const float vt = v_s[t][vl];
             float o = 0.f;
@@ -214,14 +264,15 @@ delta_scan_kernel(const float* __restrict__ qkv, long long ldq, int q_off, int k
                   const void* __restrict__ A_log, const void* __restrict__ dt_bias, int p_dtype,
                   float* __restrict__ state, long long state_stride, const int* __restrict__ spans,
                   const int* __restrict__ tok_slot, float* __restrict__ out, int H, int Hk, int d, int dv,
-                  float unit_eps, float q_scale) {
+                  float unit_eps, float q_scale, int vec) {
     gi_pdl_start();
     constexpr int DP = 4 * R;
-    __shared__ __align__(16) float q_s[SCAN_TC][DP];
-    __shared__ __align__(16) float k_s[SCAN_TC][DP];
-    __shared__ float v_s[SCAN_TC][SCAN_VS];
-    __shared__ float o_s[SCAN_TC][SCAN_VS];
-    __shared__ float g_s[SCAN_TC], b_s[SCAN_TC];
+    constexpr int TC = SCAN_TC(R);
+    __shared__ __align__(16) float q_s[TC][DP];
+    __shared__ __align__(16) float k_s[TC][DP];
+    __shared__ float v_s[TC][SCAN_VS];
+    __shared__ float o_s[TC][SCAN_VS];
+    __shared__ float g_s[TC], b_s[TC];
     int slot, start, len;
     scan_span(spans, tok_slot, blockIdx.x, slot, start, len);
     const int h = blockIdx.y, v0 = blockIdx.z * SCAN_VS;
@@ -242,28 +293,55 @@ delta_scan_kernel(const float* __restrict__ qkv, long long ldq, int q_off, int k
 #pragma unroll
         for (int e = 0; e < R; ++e) S[e] = 0.f;
     }
-    for (int t0 = 0; t0 < len; t0 += SCAN_TC) {
-        const int tc = min(SCAN_TC, len - t0);
+    for (int t0 = 0; t0 < len; t0 += TC) {
+        const int tc = min(TC, len - t0);
         __syncthreads();
-        // each warp stages tokens warp, warp + 4: q and k as unit vectors (sum of squares in lane order, then a tree)
-        for (int t = warp; t < tc; t += SCAN_THREADS / 32) {
+        // each warp stages tokens warp, warp + 4, ...: first the raw q, k and v of all its tokens (independent
+        // loads, 16 bytes at a time when the rows allow it), then q and k as unit vectors (sum of squares: a
+        // lane's elements in order, then a tree over the lanes)
+        constexpr int TPW = TC / (SCAN_THREADS / 32);
+        float sq[TPW], sk[TPW];
+#pragma unroll
+        for (int i = 0; i < TPW; ++i) {
+            const int t = warp + (SCAN_THREADS / 32) * i;
+            sq[i] = 0.f; sk[i] = 0.f;
+            if (t >= tc) continue;
             const float* row = qkv + (size_t)(start + t0 + t) * ldq;
-            float sq = 0.f, sk = 0.f;
-            for (int c = lane; c < DP; c += 32) {
-                const float qv = c < d ? row[q_off + kh * d + c] : 0.f;
-                const float kv = c < d ? row[k_off + kh * d + c] : 0.f;
-                q_s[t][c] = qv; k_s[t][c] = kv;
-                sq = fmaf(qv, qv, sq); sk = fmaf(kv, kv, sk);
+            if (vec) {
+                for (int c4 = lane; c4 < DP / 4; c4 += 32) {
+                    float4 qv = make_float4(0.f, 0.f, 0.f, 0.f), kv = qv;
+                    if (c4 * 4 < d) {
+                        qv = *reinterpret_cast<const float4*>(row + q_off + kh * d + c4 * 4);
+                        kv = *reinterpret_cast<const float4*>(row + k_off + kh * d + c4 * 4);
+                    }
+                    *reinterpret_cast<float4*>(&q_s[t][c4 * 4]) = qv;
+                    *reinterpret_cast<float4*>(&k_s[t][c4 * 4]) = kv;
+                    sq[i] = fmaf(qv.x, qv.x, sq[i]); sq[i] = fmaf(qv.y, qv.y, sq[i]);
+                    sq[i] = fmaf(qv.z, qv.z, sq[i]); sq[i] = fmaf(qv.w, qv.w, sq[i]);
+                    sk[i] = fmaf(kv.x, kv.x, sk[i]); sk[i] = fmaf(kv.y, kv.y, sk[i]);
+                    sk[i] = fmaf(kv.z, kv.z, sk[i]); sk[i] = fmaf(kv.w, kv.w, sk[i]);
+                }
+            } else {
+                for (int c = lane; c < DP; c += 32) {
+                    const float qv = c < d ? row[q_off + kh * d + c] : 0.f;
+                    const float kv = c < d ? row[k_off + kh * d + c] : 0.f;
+                    q_s[t][c] = qv; k_s[t][c] = kv;
+                    sq[i] = fmaf(qv, qv, sq[i]); sk[i] = fmaf(kv, kv, sk[i]);
+                }
             }
-            sq = warp_sum(sq); sk = warp_sum(sk);
-            const float iq = q_scale / sqrtf(sq + unit_eps), ik = 1.f / sqrtf(sk + unit_eps);
-            for (int c = lane; c < DP; c += 32) { q_s[t][c] *= iq; k_s[t][c] *= ik; }
+            v_s[t][lane] = v0 + lane < dv ? row[v_off + h * dv + v0 + lane] : 0.f;
             if (lane == 0) {
                 const float* abr = ab + (size_t)(start + t0 + t) * ldab;
                 g_s[t] = expf(-rate * rc_softplus(abr[a_off + h] + dt));
                 b_s[t] = rc_sigmoid(abr[b_off + h]);
             }
-            v_s[t][lane] = v0 + lane < dv ? row[v_off + h * dv + v0 + lane] : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < TPW; ++i) {
+            const int t = warp + (SCAN_THREADS / 32) * i;
+            if (t >= tc) continue;
+            const float iq = q_scale / sqrtf(warp_sum(sq[i]) + unit_eps), ik = 1.f / sqrtf(warp_sum(sk[i]) + unit_eps);
+            for (int c = lane; c < DP; c += 32) { q_s[t][c] *= iq; k_s[t][c] *= ik; }
         }
         __syncthreads();
         for (int t = 0; t < tc; ++t) {
@@ -335,9 +413,11 @@ extern "C" int gi_decay_scan(const void* qkv, long long ld, int act_dtype, int q
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_seq, H, (dv + SCAN_VS - 1) / SCAN_VS);
     if (act_dtype == GI_DTYPE_F32) {
-        SCAN_DISPATCH(decay_scan_kernel, float, (const float*)qkv, ld, q_off, k_off, v_off, decay, state, state_stride, spans, tok_slot, out, H, d, dv)
+        SCAN_DISPATCH(decay_scan_kernel, float, (const float*)qkv, ld, q_off, k_off, v_off, decay, state, state_stride, spans, tok_slot, out, H, d, dv, 0)
     } else if (act_dtype == GI_DTYPE_BF16) {
-        SCAN_DISPATCH(decay_scan_kernel, bf16, (const bf16*)qkv, ld, q_off, k_off, v_off, decay, state, state_stride, spans, tok_slot, out, H, d, dv)
+        const int vec_rows = d % 8 == 0 && dv % 8 == 0 && ld % 8 == 0 && q_off % 8 == 0 && k_off % 8 == 0 && v_off % 8 == 0 &&
+                             (uintptr_t)qkv % 16 == 0;
+        SCAN_DISPATCH(decay_scan_kernel, bf16, (const bf16*)qkv, ld, q_off, k_off, v_off, decay, state, state_stride, spans, tok_slot, out, H, d, dv, vec_rows)
     } else {
         GI_REQUIRE(false, "gi_decay_scan: activation dtype %d", act_dtype);
     }
@@ -358,6 +438,7 @@ extern "C" int gi_delta_scan(const float* qkv, long long ldq, int q_off, int k_o
     if (n_seq == 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_seq, H, (dv + SCAN_VS - 1) / SCAN_VS);
-    SCAN_DISPATCH(delta_scan_kernel, float, qkv, ldq, q_off, k_off, v_off, ab, ldab, b_off, a_off, A_log, dt_bias, p_dtype, state, state_stride, spans, tok_slot, out, H, Hk, d, dv, unit_eps, q_scale)
+    const int vec = d % 4 == 0 && ldq % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 && (uintptr_t)qkv % 16 == 0;
+    SCAN_DISPATCH(delta_scan_kernel, float, qkv, ldq, q_off, k_off, v_off, ab, ldab, b_off, a_off, A_log, dt_bias, p_dtype, state, state_stride, spans, tok_slot, out, H, Hk, d, dv, unit_eps, q_scale, vec)
     return gi_check_launch("gi_delta_scan");
 }
