@@ -46,8 +46,7 @@ _MIXER_KEYS = {
 
 
 def _typed(d: dict, keys: dict, where: str) -> dict:
-    """The listed keys of `d`, each of its type.  A key this library does not know is left out with a warning:
-    the design says that what its description does not mention does not exist."""
+    """The listed keys of `d`, each of its type.  A key this library does not know is left out with a warning."""
     if not isinstance(d, dict):
         raise ConfigError(f"{where}: must be an object, found {d!r}")
     unknown = sorted(set(d) - set(keys))

@@ -38,8 +38,8 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ x, long long ldx, 
                                         int taps_dtype, int K, const float* __restrict__ state, long long state_stride,
                                         const int* __restrict__ tok_slot, float* __restrict__ out) {
     gi_pdl_start();
-    const int r = blockIdx.y;
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int r = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= C) return;
     const int slot = tok_slot[r];
     const int have = slot < 0 ? 0 : rows_before(tok_slot, r, slot, K - 1);
@@ -58,8 +58,8 @@ __global__ void conv_state_update_kernel(const T* __restrict__ x, long long ldx,
                                          float* __restrict__ state, long long state_stride,
                                          const int* __restrict__ tok_slot, int n_rows) {
     gi_pdl_start();
-    const int r = blockIdx.y;
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int r = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= C) return;
     const int slot = tok_slot[r];
     if (slot < 0 || (r + 1 < n_rows && tok_slot[r + 1] == slot)) return;      // only a sequence's last row acts
@@ -79,10 +79,10 @@ extern "C" int gi_causal_conv_silu(const void* x, long long ldx, int act_dtype, 
     GI_REQUIRE(n_rows >= 0 && C > 0 && K >= 1 && K <= CONV_MAX_TAPS, "gi_causal_conv_silu: %d channels, %d taps (1 to %d)",
                C, K, CONV_MAX_TAPS);
     GI_REQUIRE(ldx >= C && state_stride >= (long long)(K - 1) * C, "gi_causal_conv_silu: strides shorter than the rows");
-    GI_REQUIRE(n_rows <= 65535, "gi_causal_conv_silu: %d rows in one step is beyond 65535", n_rows);
+    GI_REQUIRE((C + 127) / 128 <= 65535, "gi_causal_conv_silu: %d channels is beyond %d", C, 65535 * 128);
     if (n_rows == 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    dim3 grid((C + 127) / 128, n_rows);
+    dim3 grid(n_rows, (C + 127) / 128);
     if (act_dtype == GI_DTYPE_F32) {
         if (!update_state) gi_launch(causal_conv_silu_kernel<float>, grid, dim3(128), 0, s, (const float*)x, ldx, C, taps, taps_dtype, K, (const float*)state, state_stride, tok_slot, out);
         else if (K > 1) gi_launch(conv_state_update_kernel<float>, grid, dim3(128), 0, s, (const float*)x, ldx, C, K, state, state_stride, tok_slot, n_rows);
@@ -230,17 +230,17 @@ decay_scan_kernel(const T* __restrict__ qkv, long long ld, int q_off, int k_off,
         if (vec && t0 + TC < len) fetch(t0 + TC);
         for (int t = 0; t < tc; ++t) {
             const float vt = v_s[t][vl];
-            float o = 0.f;
+            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;     // four chains instead of one of R dependent steps
 #pragma unroll
             for (int i = 0; i < R / 4; ++i) {
                 const float4 kk = *reinterpret_cast<const float4*>(&k_s[t][KEY_OF(i, part)]);
                 const float4 qq = *reinterpret_cast<const float4*>(&q_s[t][KEY_OF(i, part)]);
-                S[4 * i] = fmaf(lam, S[4 * i], kk.x * vt);          o = fmaf(S[4 * i], qq.x, o);
-                S[4 * i + 1] = fmaf(lam, S[4 * i + 1], kk.y * vt);  o = fmaf(S[4 * i + 1], qq.y, o);
-                S[4 * i + 2] = fmaf(lam, S[4 * i + 2], kk.z * vt);  o = fmaf(S[4 * i + 2], qq.z, o);
-                S[4 * i + 3] = fmaf(lam, S[4 * i + 3], kk.w * vt);  o = fmaf(S[4 * i + 3], qq.w, o);
+                S[4 * i] = fmaf(lam, S[4 * i], kk.x * vt);          o0 = fmaf(S[4 * i], qq.x, o0);
+                S[4 * i + 1] = fmaf(lam, S[4 * i + 1], kk.y * vt);  o1 = fmaf(S[4 * i + 1], qq.y, o1);
+                S[4 * i + 2] = fmaf(lam, S[4 * i + 2], kk.z * vt);  o2 = fmaf(S[4 * i + 2], qq.z, o2);
+                S[4 * i + 3] = fmaf(lam, S[4 * i + 3], kk.w * vt);  o3 = fmaf(S[4 * i + 3], qq.w, o3);
             }
-            o = quad_sum(o);
+            const float o = quad_sum((o0 + o1) + (o2 + o3));
             if (part == 0) o_s[t][vl] = o;
         }
         __syncthreads();
@@ -346,28 +346,28 @@ delta_scan_kernel(const float* __restrict__ qkv, long long ldq, int q_off, int k
         __syncthreads();
         for (int t = 0; t < tc; ++t) {
             const float g = g_s[t];
-            float r = 0.f;
+            float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;     // four chains instead of one of R dependent steps
 #pragma unroll
             for (int i = 0; i < R / 4; ++i) {
                 const float4 kk = *reinterpret_cast<const float4*>(&k_s[t][KEY_OF(i, part)]);
-                S[4 * i] *= g;      r = fmaf(S[4 * i], kk.x, r);
-                S[4 * i + 1] *= g;  r = fmaf(S[4 * i + 1], kk.y, r);
-                S[4 * i + 2] *= g;  r = fmaf(S[4 * i + 2], kk.z, r);
-                S[4 * i + 3] *= g;  r = fmaf(S[4 * i + 3], kk.w, r);
+                S[4 * i] *= g;      r0 = fmaf(S[4 * i], kk.x, r0);
+                S[4 * i + 1] *= g;  r1 = fmaf(S[4 * i + 1], kk.y, r1);
+                S[4 * i + 2] *= g;  r2 = fmaf(S[4 * i + 2], kk.z, r2);
+                S[4 * i + 3] *= g;  r3 = fmaf(S[4 * i + 3], kk.w, r3);
             }
-            r = quad_sum(r);
+            const float r = quad_sum((r0 + r1) + (r2 + r3));
             const float u = b_s[t] * (v_s[t][vl] - r);
-            float o = 0.f;
+            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
             for (int i = 0; i < R / 4; ++i) {
                 const float4 kk = *reinterpret_cast<const float4*>(&k_s[t][KEY_OF(i, part)]);
                 const float4 qq = *reinterpret_cast<const float4*>(&q_s[t][KEY_OF(i, part)]);
-                S[4 * i] = fmaf(kk.x, u, S[4 * i]);          o = fmaf(S[4 * i], qq.x, o);
-                S[4 * i + 1] = fmaf(kk.y, u, S[4 * i + 1]);  o = fmaf(S[4 * i + 1], qq.y, o);
-                S[4 * i + 2] = fmaf(kk.z, u, S[4 * i + 2]);  o = fmaf(S[4 * i + 2], qq.z, o);
-                S[4 * i + 3] = fmaf(kk.w, u, S[4 * i + 3]);  o = fmaf(S[4 * i + 3], qq.w, o);
+                S[4 * i] = fmaf(kk.x, u, S[4 * i]);          o0 = fmaf(S[4 * i], qq.x, o0);
+                S[4 * i + 1] = fmaf(kk.y, u, S[4 * i + 1]);  o1 = fmaf(S[4 * i + 1], qq.y, o1);
+                S[4 * i + 2] = fmaf(kk.z, u, S[4 * i + 2]);  o2 = fmaf(S[4 * i + 2], qq.z, o2);
+                S[4 * i + 3] = fmaf(kk.w, u, S[4 * i + 3]);  o3 = fmaf(S[4 * i + 3], qq.w, o3);
             }
-            o = quad_sum(o);
+            const float o = quad_sum((o0 + o1) + (o2 + o3));
             if (part == 0) o_s[t][vl] = o;
         }
         __syncthreads();
