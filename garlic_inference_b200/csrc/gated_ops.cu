@@ -18,6 +18,76 @@ __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
 // ------------------------------------------------------------------ gate, norm, add
+// Eight consecutive values starting at element c (a multiple of 8, the base on 16 bytes) as float32.
+__device__ __forceinline__ void load8(const float* p, int c, float* out) {
+    const float4 a = *reinterpret_cast<const float4*>(p + c), b = *reinterpret_cast<const float4*>(p + c + 4);
+    out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w; out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+}
+__device__ __forceinline__ void load8(const bf16* p, int c, float* out) {
+    const uint4 w = *reinterpret_cast<const uint4*>(p + c);
+    const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&w);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(p2[i]); out[2 * i] = f.x; out[2 * i + 1] = f.y; }
+}
+__device__ __forceinline__ void load8_w(const void* w, int w_dtype, int c, float* out) {
+    if (w_dtype == GI_DTYPE_F32) load8((const float*)w, c, out); else load8((const bf16*)w, c, out);
+}
+__device__ __forceinline__ void store8(float* p, int c, const float* v) {
+    *reinterpret_cast<float4*>(p + c) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + c + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void store8(bf16* p, int c, const float* v) {
+    uint4 w;
+    __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) p2[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p + c) = w;
+}
+
+// The same arithmetic as the kernel below, element for element, with 16-byte loads and stores (a thread sums
+// eight consecutive elements at a time, then the block's tree): taken when the rows allow it, which depends
+// on the sizes and the tensors' alignment alone, never on how a request was cut.  A decode step runs this kernel twice per layer on a handful of rows, where it is a chain of
+// memory latencies, so the fewer and wider its loads the better.
+template <typename T>
+__global__ void gate_norm_add_vec_kernel(const T* __restrict__ y, long long ldy, const T* __restrict__ g, long long ldg,
+                                         const void* __restrict__ bias, int b_dtype, const void* __restrict__ weight,
+                                         int w_dtype, float* __restrict__ residual, T* __restrict__ act_out, int dim,
+                                         float eps) {
+    gi_pdl_start();
+    extern __shared__ float row[];
+    float* red = row + dim;
+    const size_t r = blockIdx.x;
+    const T* yr = y + r * ldy;
+    const T* gr = g ? g + r * ldg : nullptr;
+    float ss = 0.f;
+#pragma unroll 2
+    for (int c = threadIdx.x * 8; c < dim; c += blockDim.x * 8) {
+        float s[8], z[8], b[8];
+        load8(yr, c, s);
+        if (gr) {
+            load8(gr, c, z);
+            if (bias) load8_w(bias, b_dtype, c, b);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s[i] *= sigmoid_f(z[i] + (bias ? b[i] : 0.f));
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { row[c + i] = s[i]; ss += s[i] * s[i]; }
+    }
+    ss = block_sum(ss, red);
+    const float inv = 1.f / sqrtf(ss / (float)dim + eps);
+    float* res = residual + r * dim;
+#pragma unroll 2
+    for (int c = threadIdx.x * 8; c < dim; c += blockDim.x * 8) {
+        float x[8], w[8];
+        load8(res, c, x);
+        load8_w(weight, w_dtype, c, w);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] += row[c + i] * inv * w[i];
+        store8(res, c, x);
+        if (act_out) store8(act_out + r * dim, c, x);
+    }
+}
+
 template <typename T>
 __global__ void gate_norm_add_kernel(const T* __restrict__ y, long long ldy, const T* __restrict__ g, long long ldg,
                                      const void* __restrict__ bias, int b_dtype, const void* __restrict__ weight,
@@ -30,6 +100,8 @@ __global__ void gate_norm_add_kernel(const T* __restrict__ y, long long ldy, con
     const T* yr = y + r * ldy;
     const T* gr = g ? g + r * ldg : nullptr;
     float ss = 0.f;
+    // unrolled: a few rows at a time are one chain of memory latencies, so the loads of several iterations go out together
+#pragma unroll 8
     for (int c = threadIdx.x; c < dim; c += blockDim.x) {
         float s = to_f32(yr[c]);
         if (gr) s *= sigmoid_f(to_f32(gr[c]) + (bias ? load_w(bias, b_dtype, c) : 0.f));
@@ -39,6 +111,7 @@ __global__ void gate_norm_add_kernel(const T* __restrict__ y, long long ldy, con
     ss = block_sum(ss, red);
     const float inv = 1.f / sqrtf(ss / (float)dim + eps);
     float* res = residual + r * dim;
+#pragma unroll 8
     for (int c = threadIdx.x; c < dim; c += blockDim.x) {
         const float x = res[c] + row[c] * inv * load_w(weight, w_dtype, c);
         res[c] = x;
@@ -52,10 +125,19 @@ extern "C" int gi_gate_norm_add(const void* y, long long ldy, const void* g, lon
     GI_REQUIRE(n_rows >= 0 && dim > 0 && dim <= 16384, "gi_gate_norm_add: rows of %d elements (at most 16384)", dim);
     GI_REQUIRE(ldy >= dim && (!g || ldg >= dim), "gi_gate_norm_add: row strides shorter than the rows");
     if (n_rows == 0) return 0;
-    const int threads = dim >= 1024 ? 256 : 128;
+    const int threads = dim >= 4096 ? 512 : (dim >= 1024 ? 256 : 128);
     const size_t smem = ((size_t)dim + 33) * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
-    if (act_dtype == GI_DTYPE_F32) {
+    auto on16 = [](const void* p) { return p == nullptr || (uintptr_t)p % 16 == 0; };
+    const bool vec = dim % 8 == 0 && ldy % 8 == 0 && (!g || ldg % 8 == 0) && on16(y) && on16(g) && on16(bias) &&
+                     on16(weight) && on16(residual) && on16(act_out) && smem <= 48 * 1024;
+    if (vec && act_dtype == GI_DTYPE_F32) {
+        gi_launch(gate_norm_add_vec_kernel<float>, dim3(n_rows), dim3(threads), smem, s, (const float*)y, ldy, (const float*)g,
+                  ldg, bias, b_dtype, weight, w_dtype, residual, (float*)act_out, dim, eps);
+    } else if (vec && act_dtype == GI_DTYPE_BF16) {
+        gi_launch(gate_norm_add_vec_kernel<bf16>, dim3(n_rows), dim3(threads), smem, s, (const bf16*)y, ldy, (const bf16*)g,
+                  ldg, bias, b_dtype, weight, w_dtype, residual, (bf16*)act_out, dim, eps);
+    } else if (act_dtype == GI_DTYPE_F32) {
         if (smem > 48 * 1024) { int rc = gi_reserve_smem((const void*)gate_norm_add_kernel<float>, smem, "gi_gate_norm_add"); if (rc) return rc; }
         gi_launch(gate_norm_add_kernel<float>, dim3(n_rows), dim3(threads), smem, s, (const float*)y, ldy, (const float*)g,
                   ldg, bias, b_dtype, weight, w_dtype, residual, (float*)act_out, dim, eps);
@@ -115,9 +197,11 @@ __global__ void gated_group_rmsnorm_kernel(const float* __restrict__ o, const T*
     const int grp = blockIdx.y;
     const float* orow = o + (r * groups + grp) * gs;
     float ss = 0.f;
+#pragma unroll 8
     for (int c = threadIdx.x; c < gs; c += blockDim.x) ss += orow[c] * orow[c];
     ss = block_sum(ss, red);
     const float inv = 1.f / sqrtf(ss / (float)gs + eps);
+#pragma unroll 8
     for (int c = threadIdx.x; c < gs; c += blockDim.x) {
         const int col = grp * gs + c;
         const float z = to_f32(g[r * ldg + col]);
@@ -134,7 +218,7 @@ extern "C" int gi_gated_group_rmsnorm(const float* o, const void* g, long long l
                "group of %d nor the row of %d", w_len, gs, groups * gs);
     GI_REQUIRE(ldg >= (long long)groups * gs && (gate_kind == 0 || gate_kind == 1), "gi_gated_group_rmsnorm: gate");
     if (n_rows == 0) return 0;
-    const int threads = gs >= 1024 ? 256 : (gs >= 128 ? 128 : (gs > 32 ? 64 : 32));
+    const int threads = gs >= 4096 ? 512 : (gs >= 1024 ? 256 : (gs >= 128 ? 128 : (gs > 32 ? 64 : 32)));
     cudaStream_t s = (cudaStream_t)stream;
     if (act_dtype == GI_DTYPE_F32)
         gi_launch(gated_group_rmsnorm_kernel<float>, dim3(n_rows, groups), dim3(threads), 0, s, o, (const float*)g, ldg,

@@ -13,8 +13,9 @@ all heads (score q'_h . c_j + rot(q_rot) . rot(kr_j), values c_j), and Wuv,h is 
 
 Which attention runs.  Everything under float32, and short portions: the exact-order kernel (scores, softmax
 and weighted sum float32, one block per token and head).  Decode steps in bfloat16: the shared-rows kernel,
-which stages the cached rows in shared memory once for all heads and cuts the keys into slices (float32
-scores, softmax and sums as well).  Portions of `PRODUCT_MIN_ROWS`
+which stages the cached rows in shared memory once for 32 heads (asynchronous copies, a chunk ahead), cuts the
+keys into slices and does both products on tensor cores (mma.sync; float32 scores, softmax and sums, the
+weights rounded to bfloat16 as the second product's operand).  Portions of `PRODUCT_MIN_ROWS`
 tokens and more in bfloat16: because all heads share the cached rows, the scores of a block of tokens are one
 matrix product [tokens x heads, row] . [row, keys] with float32 results, the softmax (causal, with the sink,
 float32) is this package's kernel, and the weighted sum is a second product [tokens x heads, keys] . [keys,
