@@ -12,10 +12,15 @@
 //
 // A scan block owns one (sequence, head, slice of 32 value columns) and walks the sequence's tokens of this
 // step in order, so prompts, portions of prompts and single tokens run the same instructions in the same
-// order and give the same bits.  A thread holds, for one value column, a quarter of the key dimension in
-// registers (4 consecutive keys out of every 16); sums over the key dimension end with two shuffles.
-// State rows are laid out [head][value column][key, padded to 4 R] so that a warp's loads and stores are
-// whole 64-byte runs.  NikolayBlagoev/garlic-inference has no recurrent mixer.
+// order and give the same bits.  P lanes share one value column: a thread holds R of the column's keys in
+// registers (4 consecutive keys out of every 4 P), and sums over the keys end with log2(P) shuffles.  P is 4 or
+// 8 by the key dimension alone (8 from 64 keys on): with one long prompt there are only heads x columns / 32
+// blocks, and it is the warps of a block that hide each other's latencies.  Measured at keys of 128, 32 heads
+// (P = 4 / 8 / 16): a prompt of 2,048 tokens 0.91 / 0.71 / 0.70 ms (decay) and 1.61 / 1.23 / 1.04 ms (delta rule); a
+// whole decode step of 64 sequences 1.72 / 1.80 / 1.89 ms.  P never depends on the batch or the cut, so a
+// position's bits do not either.
+// State rows are laid out [head][value column][key, padded to R P] so that a warp's loads and stores are
+// whole runs of 16 P bytes.  NikolayBlagoev/garlic-inference has no recurrent mixer.
 #include "common.cuh"
 #include <math.h>
 
@@ -99,9 +104,8 @@ extern "C" int gi_causal_conv_silu(const void* x, long long ldx, int act_dtype, 
 // Tokens staged in shared memory at a time: 32 (16 for the widest keys, to stay inside 48 KB).  A chunk costs one
 // round trip to global memory that nothing hides when a block has its SM to itself (one long prompt), so the
 // chunk is as long as shared memory allows; the results do not depend on it.
-#define SCAN_TC(R) ((R) <= 32 ? 32 : 16)
-#define SCAN_VS 32           // value columns per block
-#define SCAN_THREADS 128
+#define SCAN_TC(DP) ((DP) <= 128 ? 32 : 16)
+#define SCAN_VS 32           // value columns per block; a block has 32 P threads
 
 // Where a sequence's rows are: from `spans` [n_seq, 3] = {slot, first row, rows}, or, without spans, sequence
 // i is row i alone (a decode step: the slot comes from tok_slot).
@@ -111,10 +115,10 @@ __device__ __forceinline__ void scan_span(const int* __restrict__ spans, const i
     else { slot = tok_slot[seq]; start = seq; len = 1; }
 }
 
-// A thread's R state values: register e = 4 i + w holds key (4 i + part) * 4 + w of its value column.
-#define KEY_OF(i, part) (((i) * 4 + (part)) * 4)
+// A thread's R state values: register e = 4 i + w holds key (P i + part) * 4 + w of its value column.
+#define KEY_OF(i, part) (((i) * P + (part)) * 4)
 
-template <int R>
+template <int R, int P>
 __device__ __forceinline__ void scan_load_state(float (&S)[R], const float* __restrict__ st, int part) {
 #pragma unroll
     for (int i = 0; i < R / 4; ++i) {
@@ -122,30 +126,32 @@ __device__ __forceinline__ void scan_load_state(float (&S)[R], const float* __re
         S[4 * i] = v.x; S[4 * i + 1] = v.y; S[4 * i + 2] = v.z; S[4 * i + 3] = v.w;
     }
 }
-template <int R>
+template <int R, int P>
 __device__ __forceinline__ void scan_store_state(const float (&S)[R], float* __restrict__ st, int part) {
 #pragma unroll
     for (int i = 0; i < R / 4; ++i)
         *reinterpret_cast<float4*>(st + KEY_OF(i, part)) = make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]);
 }
-__device__ __forceinline__ float quad_sum(float v) {
-    v += __shfl_xor_sync(0xffffffffu, v, 1);
-    v += __shfl_xor_sync(0xffffffffu, v, 2);
+template <int P>
+__device__ __forceinline__ float part_sum(float v) {               // over the P lanes of one value column
+#pragma unroll
+    for (int o = 1; o < P; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
 
 // ---- linear attention with a fixed decay per head
 // qkv: T [n, ld], silu applied here; q at column q_off + h d, k at k_off + h d, v at v_off + h dv.
-template <typename T, int R>
-__global__ void __launch_bounds__(SCAN_THREADS)
+template <typename T, int R, int P>
+__global__ void __launch_bounds__(SCAN_VS * P)
 decay_scan_kernel(const T* __restrict__ qkv, long long ld, int q_off, int k_off, int v_off,
                   const float* __restrict__ decay, float* __restrict__ state, long long state_stride,
                   const int* __restrict__ spans, const int* __restrict__ tok_slot, float* __restrict__ out,
                   int H, int d, int dv, int vec_rows) {
     gi_pdl_start();
     const bool vec = sizeof(T) == 2 && vec_rows;       // rows that can be fetched 16 bytes at a time
-    constexpr int DP = 4 * R;                          // padded key dimension
-    constexpr int TC = SCAN_TC(R);
+    constexpr int DP = R * P;                          // padded key dimension
+    constexpr int TC = SCAN_TC(DP);
+    constexpr int SCAN_THREADS = SCAN_VS * P;
     __shared__ __align__(16) float q_s[TC][DP];
     __shared__ __align__(16) float k_s[TC][DP];
     __shared__ float v_s[TC][SCAN_VS];
@@ -154,7 +160,7 @@ decay_scan_kernel(const T* __restrict__ qkv, long long ld, int q_off, int k_off,
     scan_span(spans, tok_slot, blockIdx.x, slot, start, len);
     const int h = blockIdx.y, v0 = blockIdx.z * SCAN_VS;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int part = lane & 3, vl = warp * 8 + (lane >> 2), v = v0 + vl;
+    const int part = threadIdx.x % P, vl = threadIdx.x / P, v = v0 + vl;
     const bool live = v < dv;
     if (slot < 0) {
         for (int t = 0; t < len; ++t)
@@ -164,7 +170,7 @@ decay_scan_kernel(const T* __restrict__ qkv, long long ld, int q_off, int k_off,
     const float lam = decay[h];
     float* st = state + (size_t)slot * state_stride + ((size_t)h * dv + (live ? v : 0)) * DP;
     float S[R];
-    if (live) scan_load_state<R>(S, st, part);
+    if (live) scan_load_state<R, P>(S, st, part);
     else {
 #pragma unroll
         for (int e = 0; e < R; ++e) S[e] = 0.f;
@@ -240,7 +246,7 @@ decay_scan_kernel(const T* __restrict__ qkv, long long ld, int q_off, int k_off,
                 S[4 * i + 2] = fmaf(lam, S[4 * i + 2], kk.z * vt);  o2 = fmaf(S[4 * i + 2], qq.z, o2);
                 S[4 * i + 3] = fmaf(lam, S[4 * i + 3], kk.w * vt);  o3 = fmaf(S[4 * i + 3], qq.w, o3);
             }
-            const float o = quad_sum((o0 + o1) + (o2 + o3));
+            const float o = part_sum<P>((o0 + o1) + (o2 + o3));
             if (part == 0) o_s[t][vl] = o;
         }
         __syncthreads();
@@ -249,7 +255,7 @@ decay_scan_kernel(const T* __restrict__ qkv, long long ld, int q_off, int k_off,
             if (v0 + c < dv) out[(size_t)(start + t0 + t) * H * dv + h * dv + v0 + c] = o_s[t][c];
         }
     }
-    if (live) scan_store_state<R>(S, st, part);
+    if (live) scan_store_state<R, P>(S, st, part);
 }
 
 // ---- the gated delta rule
@@ -257,8 +263,8 @@ decay_scan_kernel(const T* __restrict__ qkv, long long ld, int q_off, int k_off,
 // head h at v_off + h dv.  ab: float32 [n, ldab]: beta's logit of head h at column b_off + h, the decay's at
 // a_off + h (float32 whatever the activation type is: the decay's logit is multiplied by exp(A_h) and goes
 // through two exponentials, which would magnify a 16-bit rounding).
-template <typename T, int R>
-__global__ void __launch_bounds__(SCAN_THREADS)
+template <typename T, int R, int P>
+__global__ void __launch_bounds__(SCAN_VS * P)
 delta_scan_kernel(const float* __restrict__ qkv, long long ldq, int q_off, int k_off, int v_off,
                   const float* __restrict__ ab, long long ldab, int b_off, int a_off,
                   const void* __restrict__ A_log, const void* __restrict__ dt_bias, int p_dtype,
@@ -266,8 +272,9 @@ delta_scan_kernel(const float* __restrict__ qkv, long long ldq, int q_off, int k
                   const int* __restrict__ tok_slot, float* __restrict__ out, int H, int Hk, int d, int dv,
                   float unit_eps, float q_scale, int vec) {
     gi_pdl_start();
-    constexpr int DP = 4 * R;
-    constexpr int TC = SCAN_TC(R);
+    constexpr int DP = R * P;
+    constexpr int TC = SCAN_TC(DP);
+    constexpr int SCAN_THREADS = SCAN_VS * P;
     __shared__ __align__(16) float q_s[TC][DP];
     __shared__ __align__(16) float k_s[TC][DP];
     __shared__ float v_s[TC][SCAN_VS];
@@ -278,7 +285,7 @@ delta_scan_kernel(const float* __restrict__ qkv, long long ldq, int q_off, int k
     const int h = blockIdx.y, v0 = blockIdx.z * SCAN_VS;
     const int kh = h / (H / Hk);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int part = lane & 3, vl = warp * 8 + (lane >> 2), v = v0 + vl;
+    const int part = threadIdx.x % P, vl = threadIdx.x / P, v = v0 + vl;
     const bool live = v < dv;
     if (slot < 0) {
         for (int t = 0; t < len; ++t)
@@ -288,7 +295,7 @@ delta_scan_kernel(const float* __restrict__ qkv, long long ldq, int q_off, int k
     const float rate = expf(load_w(A_log, p_dtype, h)), dt = load_w(dt_bias, p_dtype, h);
     float* st = state + (size_t)slot * state_stride + ((size_t)h * dv + (live ? v : 0)) * DP;
     float S[R];
-    if (live) scan_load_state<R>(S, st, part);
+    if (live) scan_load_state<R, P>(S, st, part);
     else {
 #pragma unroll
         for (int e = 0; e < R; ++e) S[e] = 0.f;
@@ -355,7 +362,7 @@ delta_scan_kernel(const float* __restrict__ qkv, long long ldq, int q_off, int k
                 S[4 * i + 2] *= g;  r2 = fmaf(S[4 * i + 2], kk.z, r2);
                 S[4 * i + 3] *= g;  r3 = fmaf(S[4 * i + 3], kk.w, r3);
             }
-            const float r = quad_sum((r0 + r1) + (r2 + r3));
+            const float r = part_sum<P>((r0 + r1) + (r2 + r3));
             const float u = b_s[t] * (v_s[t][vl] - r);
             float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
@@ -367,7 +374,7 @@ delta_scan_kernel(const float* __restrict__ qkv, long long ldq, int q_off, int k
                 S[4 * i + 2] = fmaf(kk.z, u, S[4 * i + 2]);  o2 = fmaf(S[4 * i + 2], qq.z, o2);
                 S[4 * i + 3] = fmaf(kk.w, u, S[4 * i + 3]);  o3 = fmaf(S[4 * i + 3], qq.w, o3);
             }
-            const float o = quad_sum((o0 + o1) + (o2 + o3));
+            const float o = part_sum<P>((o0 + o1) + (o2 + o3));
             if (part == 0) o_s[t][vl] = o;
         }
         __syncthreads();
@@ -376,39 +383,41 @@ delta_scan_kernel(const float* __restrict__ qkv, long long ldq, int q_off, int k
             if (v0 + c < dv) out[(size_t)(start + t0 + t) * H * dv + h * dv + v0 + c] = o_s[t][c];
         }
     }
-    if (live) scan_store_state<R>(S, st, part);
+    if (live) scan_store_state<R, P>(S, st, part);
 }
 
-// Registers per thread for a key dimension: the smallest of 4, 8, 16, 32, 64 with 4 R >= d (0: too large).
-static int scan_regs(int d) {
-    for (int r = 4; r <= 64; r *= 2)
-        if (4 * r >= d) return r;
+// The padded key dimension for d: 16, 32, 64, 128 or 256 (0: too large).
+static int scan_padded(int d) {
+    for (int dp = 16; dp <= 256; dp *= 2)
+        if (dp >= d) return dp;
     return 0;
 }
 
 // Floats of one head's state for key dimension d and value dimension dv, as the scans lay it out.
 extern "C" long long gi_scan_state_floats(int d, int dv) {
-    const int r = scan_regs(d);
-    return r ? (long long)dv * 4 * r : -1;
+    const int dp = scan_padded(d);
+    return dp ? (long long)dv * dp : -1;
 }
 
-#define SCAN_DISPATCH(KERNEL, TT, ...)                                                         \
-    switch (R) {                                                                               \
-        case 4:  gi_launch(KERNEL<TT, 4>, grid, dim3(SCAN_THREADS), 0, s, __VA_ARGS__); break;  \
-        case 8:  gi_launch(KERNEL<TT, 8>, grid, dim3(SCAN_THREADS), 0, s, __VA_ARGS__); break;  \
-        case 16: gi_launch(KERNEL<TT, 16>, grid, dim3(SCAN_THREADS), 0, s, __VA_ARGS__); break; \
-        case 32: gi_launch(KERNEL<TT, 32>, grid, dim3(SCAN_THREADS), 0, s, __VA_ARGS__); break; \
-        default: gi_launch(KERNEL<TT, 64>, grid, dim3(SCAN_THREADS), 0, s, __VA_ARGS__); break; \
+// (registers, lanes per column) by padded key dimension: 16 -> (4, 4), 32 -> (8, 4), 64 -> (8, 8), 128 -> (16, 8),
+// 256 -> (32, 8)
+#define SCAN_DISPATCH(KERNEL, TT, ...)                                                                   \
+    switch (DP) {                                                                                        \
+        case 16:  gi_launch(KERNEL<TT, 4, 4>, grid, dim3(SCAN_VS * 4), 0, s, __VA_ARGS__); break;        \
+        case 32:  gi_launch(KERNEL<TT, 8, 4>, grid, dim3(SCAN_VS * 4), 0, s, __VA_ARGS__); break;        \
+        case 64:  gi_launch(KERNEL<TT, 8, 8>, grid, dim3(SCAN_VS * 8), 0, s, __VA_ARGS__); break;        \
+        case 128: gi_launch(KERNEL<TT, 16, 8>, grid, dim3(SCAN_VS * 8), 0, s, __VA_ARGS__); break;       \
+        default:  gi_launch(KERNEL<TT, 32, 8>, grid, dim3(SCAN_VS * 8), 0, s, __VA_ARGS__); break;       \
     }
 
 extern "C" int gi_decay_scan(const void* qkv, long long ld, int act_dtype, int q_off, int k_off, int v_off,
                              const float* decay, float* state, long long state_stride, const int* spans,
                              const int* tok_slot, float* out, int n_seq, int H, int d, int dv, void* stream) {
-    const int R = scan_regs(d);
-    GI_REQUIRE(n_seq >= 0 && H > 0 && d > 0 && dv > 0 && R > 0, "gi_decay_scan: key dimension %d (at most 256)", d);
+    const int DP = scan_padded(d);
+    GI_REQUIRE(n_seq >= 0 && H > 0 && d > 0 && dv > 0 && DP > 0, "gi_decay_scan: key dimension %d (at most 256)", d);
     GI_REQUIRE(H <= 65535 && (dv + SCAN_VS - 1) / SCAN_VS <= 65535, "gi_decay_scan: %d heads of %d values", H, dv);
-    GI_REQUIRE(state_stride >= (long long)H * dv * 4 * R && state_stride % 4 == 0, "gi_decay_scan: state rows of %lld "
-               "floats are shorter than %lld or no multiple of 4", state_stride, (long long)H * dv * 4 * R);
+    GI_REQUIRE(state_stride >= (long long)H * dv * DP && state_stride % 4 == 0, "gi_decay_scan: state rows of %lld "
+               "floats are shorter than %lld or no multiple of 4", state_stride, (long long)H * dv * DP);
     if (n_seq == 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_seq, H, (dv + SCAN_VS - 1) / SCAN_VS);
@@ -429,12 +438,12 @@ extern "C" int gi_delta_scan(const float* qkv, long long ldq, int q_off, int k_o
                              int p_dtype, float* state, long long state_stride, const int* spans, const int* tok_slot,
                              float* out, int n_seq, int H, int Hk, int d, int dv, float unit_eps, float q_scale,
                              void* stream) {
-    const int R = scan_regs(d);
-    GI_REQUIRE(n_seq >= 0 && H > 0 && Hk > 0 && H % Hk == 0 && d > 0 && dv > 0 && R > 0,
+    const int DP = scan_padded(d);
+    GI_REQUIRE(n_seq >= 0 && H > 0 && Hk > 0 && H % Hk == 0 && d > 0 && dv > 0 && DP > 0,
                "gi_delta_scan: %d heads on %d key heads, key dimension %d (at most 256)", H, Hk, d);
     GI_REQUIRE(H <= 65535 && (dv + SCAN_VS - 1) / SCAN_VS <= 65535, "gi_delta_scan: %d heads of %d values", H, dv);
-    GI_REQUIRE(state_stride >= (long long)H * dv * 4 * R && state_stride % 4 == 0, "gi_delta_scan: state rows of %lld "
-               "floats are shorter than %lld or no multiple of 4", state_stride, (long long)H * dv * 4 * R);
+    GI_REQUIRE(state_stride >= (long long)H * dv * DP && state_stride % 4 == 0, "gi_delta_scan: state rows of %lld "
+               "floats are shorter than %lld or no multiple of 4", state_stride, (long long)H * dv * DP);
     if (n_seq == 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_seq, H, (dv + SCAN_VS - 1) / SCAN_VS);
