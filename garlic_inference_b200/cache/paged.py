@@ -34,6 +34,12 @@ class KVRequirement:
     window: Optional[int] = None      # None: every earlier key; w: the last w keys
     planes: int = 2                   # 2: keys and values apart; 1: one row per position (a latent that keys
                                       # and values are both made from), and the view's v_pool is its k_pool
+    value_heads: Optional[int] = None   # values of a shape of their own (None: the keys' heads / head_dim):
+    value_dim: Optional[int] = None     # the value pool is then [n_pages, value_heads, page_size, value_dim]
+
+    @property
+    def value_shape(self) -> tuple:
+        return (self.value_heads or self.n_kv_heads, self.value_dim or self.head_dim)
 
 
 @dataclass(frozen=True)
@@ -42,7 +48,28 @@ class StateRequirement:
     dtype: torch.dtype = torch.float32
 
 
-Requirement = Union[KVRequirement, StateRequirement, None]
+@dataclass(frozen=True)
+class EntryRequirement:
+    """A cache entry that holds both: paged keys and values, and a state row per slot (a mixer that runs an
+    attention and a recurrence side by side, or an attention behind short convolutions)."""
+    kv: Optional[KVRequirement] = None
+    state: Optional[StateRequirement] = None
+
+
+Requirement = Union[KVRequirement, StateRequirement, EntryRequirement, None]
+
+
+def split_requirement(req) -> tuple:
+    """(paged part, state part) of any requirement."""
+    if isinstance(req, EntryRequirement):
+        return req.kv, req.state
+    if isinstance(req, KVRequirement):
+        return req, None
+    if isinstance(req, StateRequirement):
+        return None, req
+    if req is None:
+        return None, None
+    raise CacheError(f"unknown cache requirement {req!r}")
 
 
 @dataclass
@@ -70,9 +97,27 @@ class _KVGroup:
         self.host = GroupTable(n_pages, page_size, max_slots, max_pages_per_seq, req.window)
         if req.planes not in (1, 2):
             raise CacheError(f"a paged entry holds 1 or 2 rows per position, not {req.planes}")
-        self.storage = torch.zeros((len(entries), req.planes, n_pages, req.n_kv_heads, page_size, req.head_dim),
-                                   dtype=dtype, device=device)
+        self.storage = self.k_storage = self.v_storage = None
+        if req.value_shape == (req.n_kv_heads, req.head_dim) or req.planes == 1:
+            self.storage = torch.zeros((len(entries), req.planes, n_pages, req.n_kv_heads, page_size, req.head_dim),
+                                       dtype=dtype, device=device)
+        else:                                    # keys and values of different shapes: a tensor each
+            vh, vd = req.value_shape
+            self.k_storage = torch.zeros((len(entries), n_pages, req.n_kv_heads, page_size, req.head_dim),
+                                         dtype=dtype, device=device)
+            self.v_storage = torch.zeros((len(entries), n_pages, vh, page_size, vd), dtype=dtype, device=device)
         self.table = torch.full((max_slots, max_pages_per_seq), -1, dtype=torch.int32, device=device)
+
+    def pools(self, i: int) -> tuple:
+        if self.storage is not None:
+            return self.storage[i, 0], self.storage[i, self.req.planes - 1]
+        return self.k_storage[i], self.v_storage[i]
+
+    def bytes_per_token(self) -> int:
+        vh, vd = self.req.value_shape
+        per = self.req.n_kv_heads * self.req.head_dim + (vh * vd if self.req.planes == 2 else 0)
+        size = (self.storage if self.storage is not None else self.k_storage).element_size()
+        return len(self.entries) * per * size
 
     def upload(self) -> None:
         if not self.host.dirty:
@@ -117,15 +162,14 @@ class PagedCache:
         self._state_of_entry: dict[int, torch.Tensor] = {}
         by_req: dict[KVRequirement, list[int]] = {}
         for e, req in enumerate(requirements):
-            if isinstance(req, KVRequirement):
-                by_req.setdefault(req, []).append(e)
-            elif isinstance(req, StateRequirement):
+            kv_req, state_req = split_requirement(req)
+            if kv_req is not None:
+                by_req.setdefault(kv_req, []).append(e)
+            if state_req is not None:
                 # one row per slot and a spare last row: a padding row of a recorded step carries slot -1,
                 # which as an index is that spare, so it reads and writes nothing a sequence owns
-                self._state_of_entry[e] = torch.zeros((self.max_slots + 1, *req.shape), dtype=req.dtype,
+                self._state_of_entry[e] = torch.zeros((self.max_slots + 1, *state_req.shape), dtype=state_req.dtype,
                                                       device=self.device)
-            elif req is not None:
-                raise CacheError(f"cache entry {e}: unknown requirement {req!r}")
         for req, entries in by_req.items():
             g = _KVGroup(req, entries, self.n_pages, page_size, self.max_slots, self.max_pages_per_seq,
                          dtype, self.device)
@@ -196,13 +240,15 @@ class PagedCache:
         if entry not in self._kv_of_entry:
             return None
         g, i = self._kv_of_entry[entry]
-        return KVView(g.storage[i, 0], g.storage[i, g.req.planes - 1], g.table, self.page_size, g.req.window)
+        return KVView(*g.pools(i), g.table, self.page_size, g.req.window)
 
     def state_view(self, entry: int) -> Optional[torch.Tensor]:
         return self._state_of_entry.get(entry)
 
-    def view(self, entry: int) -> EntryView:
-        return EntryView(self.kv_view(entry), self.state_view(entry))
+    def view(self, entry: int, kv_entry: Optional[int] = None) -> EntryView:
+        """What a layer run sees: the state of `entry` and the paged keys and values of `kv_entry` (another entry,
+        for a layer that reads the keys and values another layer wrote), or of `entry` itself."""
+        return EntryView(self.kv_view(entry if kv_entry is None else kv_entry), self.state_view(entry))
 
     def check_status(self) -> None:
         code = int(self.status.item())
@@ -213,5 +259,4 @@ class PagedCache:
                              "the rotary table, 4 query position beyond the block table")
 
     def bytes_per_token(self) -> int:
-        return sum(g.req.planes * len(g.entries) * g.req.n_kv_heads * g.req.head_dim * g.storage.element_size()
-                   for g in self.groups)
+        return sum(g.bytes_per_token() for g in self.groups)

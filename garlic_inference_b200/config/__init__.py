@@ -3,11 +3,14 @@ from .fivitar import ARCHITECTURE as FIVITAR_ARCHITECTURE
 from .fivitar import FivitarConfig
 from .qwen3 import ARCHITECTURE as QWEN3_ARCHITECTURE
 from .qwen3 import Qwen3Config
+from .zogulorn import ARCHITECTURE as ZOGULORN_ARCHITECTURE
+from .zogulorn import ZogulornConfig
 from .registry import (architecture_name, config_class_for, known_architectures, load_config,
                        register_architecture)
 
 register_architecture(QWEN3_ARCHITECTURE, Qwen3Config)
 register_architecture(FIVITAR_ARCHITECTURE, FivitarConfig)
+register_architecture(ZOGULORN_ARCHITECTURE, ZogulornConfig)
 
-__all__ = ["ConfigError", "LayerSpec", "ModelPlan", "PartSpec", "ScheduleEntry", "Qwen3Config", "FivitarConfig",
+__all__ = ["ConfigError", "LayerSpec", "ModelPlan", "PartSpec", "ScheduleEntry", "Qwen3Config", "FivitarConfig", "ZogulornConfig",
            "architecture_name", "config_class_for", "known_architectures", "load_config", "register_architecture"]

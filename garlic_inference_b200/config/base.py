@@ -48,10 +48,14 @@ class ScheduleEntry:
     `layer` indexes ModelPlan.layers (the same layer may be named by several
     entries: its weights are then shared).  `cache` names the cache entry this
     run reads; `writes_cache` False means it only reads what another entry
-    with the same `cache` wrote earlier in the step."""
+    with the same `cache` wrote earlier in the step.  `kv_cache` names another
+    cache entry whose paged keys and values this run reads instead of having
+    its own (it writes none then), while whatever per-sequence state the layer
+    keeps stays in `cache`."""
     layer: int
     cache: int
     writes_cache: bool = True
+    kv_cache: Optional[int] = None
 
 
 @dataclass(frozen=True)

@@ -16,7 +16,17 @@
 // value, not scaled, counted once.  With d_v < d only the first d_v columns of a value row are summed and the
 // output rows are d_v wide (a cache whose rows serve as keys in full and as values in part).
 // Query head h reads key/value head h / (n_q / n_kv).  Scores, softmax and the
-// weighted sum are float32.  Upstream hands this to a library
+// weighted sum are float32.
+// Three more parameters, for mixers beside plain grouped-query attention:
+//   chunk > 0    a query at position i sees only the keys j <= i of its own chunk, floor(j / chunk) = floor(i / chunk)
+//                (chunks are counted from position 0 of the sequence);
+//   values of their own shape: the value pool has n_vh heads per page with rows of v_row elements, which may be
+//                wider or narrower than a key row;
+//   maps > 1     every head owns `maps` softmaxes over the same values (the maps of a differential attention):
+//                the n_q query rows of a token are laid out [head][map], the n_kv key heads [key head][map], and
+//                row h = head * maps + map reads key head (head / group) * maps + map and value head head / group,
+//                group = (n_q / maps) / n_vh;
+//   out_f32      the result is written as float32 whatever the activation type is (a later kernel combines maps).  Upstream hands this to a library
 // (src/src-cuda/attention/fattn.cu:74-86: scale 1/sqrt(head_dim), causal mask
 // aligned to the last key, float32 intermediates).
 #include "common.cuh"
@@ -48,30 +58,38 @@ attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const
                     const int* __restrict__ block_table, const int* __restrict__ tok_pos,
                     const int* __restrict__ tok_slot, T* __restrict__ out, int n_q, int n_kv, int d,
                     int page_size, int max_pages, int n_pool_pages, int window, float scale,
-                    const void* __restrict__ sinks, int sink_dtype, int d_v, int* __restrict__ status) {
+                    const void* __restrict__ sinks, int sink_dtype, int d_v, int* __restrict__ status,
+                    int chunk, int n_vh, int v_row, int maps, float* __restrict__ out_f32) {
     gi_pdl_start();
     extern __shared__ float smem[];
+    const int dw = d > d_v ? d : d_v;        // width of an accumulator row
     float* q_s = smem;                       // d
-    float* acc_s = smem + d;                 // AG_WARPS * d
-    float* m_s = acc_s + AG_WARPS * d;       // AG_WARPS
+    float* acc_s = smem + d;                 // AG_WARPS * dw
+    float* m_s = acc_s + AG_WARPS * dw;      // AG_WARPS
     float* l_s = m_s + AG_WARPS;             // AG_WARPS
 
     const int t = blockIdx.x, h = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    T* o = out + ((size_t)t * n_q + h) * d_v;
+    T* o = out ? out + ((size_t)t * n_q + h) * d_v : nullptr;
+    float* of = out_f32 ? out_f32 + ((size_t)t * n_q + h) * d_v : nullptr;
     const int slot = tok_slot[t];
     const int pos = tok_pos[t];
     if (slot < 0 || pos < 0 || pos / page_size >= max_pages) {
-        for (int i = threadIdx.x; i < d_v; i += blockDim.x) o[i] = from_f32<T>(0.f);
+        for (int i = threadIdx.x; i < d_v; i += blockDim.x) {
+            if (of) of[i] = 0.f; else o[i] = from_f32<T>(0.f);
+        }
         if (slot >= 0 && threadIdx.x == 0) atomicExch(status, 4);
         return;
     }
-    const int kvh = h / (n_q / n_kv);
+    const int head = h / maps, group = (n_q / maps) / n_vh;
+    const int kvh = (head / group) * maps + (h - head * maps);
+    const int vh = head / group;
     const T* qrow = q + ((size_t)t * n_q + h) * d;
     for (int i = threadIdx.x; i < d; i += blockDim.x) q_s[i] = to_f32(qrow[i]) * scale;
     __syncthreads();
 
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    if (chunk > 0) lo = max(lo, pos / chunk * chunk);
     const int* bt = block_table + (size_t)slot * max_pages;
     float m = -INFINITY, l = 0.f;
     float acc[DPL];
@@ -83,7 +101,8 @@ attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const
     for (int c = lo / 32 + warp; c <= pos / 32; c += AG_WARPS) {
         const int j = c * 32 + lane;
         const bool valid = j >= lo && j <= pos;
-        long long row = -1;                  // element offset of this lane's key/value row
+        long long row = -1;                  // element offset of this lane's key row (-1: none)
+        long long vrow = 0;                  // and of its value row
         float s = -INFINITY;
         if (valid) {
             const int page = bt[j / page_size];
@@ -91,6 +110,7 @@ attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const
                 atomicExch(status, 5);
             } else {
                 row = (((long long)page * n_kv + kvh) * page_size + (j % page_size)) * d;
+                vrow = (((long long)page * n_vh + vh) * page_size + (j % page_size)) * v_row;
                 const vec_t* kr = reinterpret_cast<const vec_t*>(k_pool + row);
                 float a = 0.f;
                 for (int i = 0; i < d / VN; ++i) a += dot_vec(kr[i], q_s + i * VN);
@@ -109,8 +129,9 @@ attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const
         for (int jj = 0; jj < 32; ++jj) {
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const long long rj = __shfl_sync(0xffffffffu, row, jj);
+            const long long vj = __shfl_sync(0xffffffffu, vrow, jj);
             if (rj < 0) continue;
-            const T* vr = v_pool + rj;
+            const T* vr = v_pool + vj;
 #pragma unroll
             for (int r = 0; r < DPL; ++r) {
                 const int i = lane + 32 * r;
@@ -122,7 +143,7 @@ attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const
 #pragma unroll
     for (int r = 0; r < DPL; ++r) {
         const int i = lane + 32 * r;
-        if (i < d) acc_s[warp * d + i] = acc[r];
+        if (i < dw) acc_s[warp * dw + i] = acc[r];
     }
     __syncthreads();
     float M = -INFINITY;
@@ -135,8 +156,9 @@ attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const
     for (int i = threadIdx.x; i < d_v; i += blockDim.x) {
         float v = 0.f;
         for (int w = 0; w < AG_WARPS; ++w)
-            if (m_s[w] != -INFINITY) v += expf(m_s[w] - M) * acc_s[w * d + i];
-        o[i] = from_f32<T>(L > 0.f ? v / L : 0.f);
+            if (m_s[w] != -INFINITY) v += expf(m_s[w] - M) * acc_s[w * dw + i];
+        const float res = L > 0.f ? v / L : 0.f;
+        if (of) of[i] = res; else o[i] = from_f32<T>(res);
     }
 }
 
@@ -144,41 +166,64 @@ template <typename T>
 static int launch_generic(const void* q, const void* k_pool, const void* v_pool, const int* block_table,
                           const int* tok_pos, const int* tok_slot, void* out, int n_tokens, int n_q, int n_kv,
                           int d, int page_size, int max_pages, int n_pool_pages, int window, float scale,
-                          const void* sinks, int sink_dtype, int d_v, int* status, cudaStream_t s) {
+                          const void* sinks, int sink_dtype, int d_v, int* status, int chunk, int n_vh, int v_row,
+                          int maps, float* out_f32, cudaStream_t s) {
     dim3 grid(n_tokens, n_q);
-    const size_t smem = ((size_t)d * (1 + AG_WARPS) + 2 * AG_WARPS) * sizeof(float);
+    const int dw = d > d_v ? d : d_v;
+    const size_t smem = ((size_t)d + (size_t)dw * AG_WARPS + 2 * AG_WARPS) * sizeof(float);
 #define AG_LAUNCH(DPL)                                                                               \
     gi_launch(attn_generic_kernel<T, DPL>, grid, dim3(AG_WARPS * 32), smem, s,                                     \
         (const T*)q, (const T*)k_pool, (const T*)v_pool, block_table, tok_pos, tok_slot, (T*)out,     \
-        n_q, n_kv, d, page_size, max_pages, n_pool_pages, window, scale, sinks, sink_dtype, d_v, status)
-    if (d <= 32) AG_LAUNCH(1);
-    else if (d <= 64) AG_LAUNCH(2);
-    else if (d <= 128) AG_LAUNCH(4);
-    else if (d <= 256) AG_LAUNCH(8);
-    else if (d <= 512) AG_LAUNCH(16);
+        n_q, n_kv, d, page_size, max_pages, n_pool_pages, window, scale, sinks, sink_dtype, d_v, status, \
+        chunk, n_vh, v_row, maps, out_f32)
+    if (dw <= 32) AG_LAUNCH(1);
+    else if (dw <= 64) AG_LAUNCH(2);
+    else if (dw <= 128) AG_LAUNCH(4);
+    else if (dw <= 256) AG_LAUNCH(8);
+    else if (dw <= 512) AG_LAUNCH(16);
     else AG_LAUNCH(32);
 #undef AG_LAUNCH
     return gi_check_launch("gi_attention_generic");
 }
 
+// The general entry point: everything the file's head lists.  `out` is written in the activation type unless
+// `out_f32` is given.  The key rows must be dense vectors of d elements (d a multiple of 8 for bfloat16, 4 for
+// float32: the vector loads); value rows may have any width.
+extern "C" int gi_attention_masked(const void* q, const void* k_pool, const void* v_pool, int act_dtype,
+                                   const int* block_table, const int* tok_pos, const int* tok_slot,
+                                   void* out, int n_tokens, int n_q, int n_kv, int d, int page_size,
+                                   int max_pages, int n_pool_pages, int window, float scale, const void* sinks,
+                                   int sink_dtype, int d_v, int* status, int chunk, int n_vh, int v_row, int maps,
+                                   float* out_f32, void* stream) {
+    GI_REQUIRE(n_tokens >= 0 && n_q > 0 && n_kv > 0 && d > 0, "gi_attention_generic: sizes must be positive");
+    GI_REQUIRE(maps >= 1 && n_vh >= 1 && n_q % maps == 0 && n_kv == n_vh * maps && (n_q / maps) % n_vh == 0,
+               "gi_attention_generic: %d query rows and %d key heads in %d maps over %d value heads", n_q, n_kv, maps, n_vh);
+    GI_REQUIRE(d % 8 == 0 && d <= 1024, "gi_attention_generic: head_dim %d must be a multiple of 8, at most 1024", d);
+    GI_REQUIRE(n_q <= 65535, "gi_attention_generic: %d query heads is beyond 65535", n_q);
+    GI_REQUIRE(d_v > 0 && d_v <= v_row && d_v <= 1024, "gi_attention_generic: %d value columns of rows of %d", d_v, v_row);
+    GI_REQUIRE(page_size > 0 && max_pages > 0 && window >= 0 && chunk >= 0, "gi_attention_generic: page size, table width, window and chunk");
+    GI_REQUIRE(out || out_f32, "gi_attention_generic: no output");
+    if (n_tokens == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (act_dtype == GI_DTYPE_F32)
+        return launch_generic<float>(q, k_pool, v_pool, block_table, tok_pos, tok_slot, out, n_tokens, n_q, n_kv, d,
+                                     page_size, max_pages, n_pool_pages, window, scale, sinks, sink_dtype, d_v, status,
+                                     chunk, n_vh, v_row, maps, out_f32, s);
+    if (act_dtype == GI_DTYPE_BF16)
+        return launch_generic<bf16>(q, k_pool, v_pool, block_table, tok_pos, tok_slot, out, n_tokens, n_q, n_kv, d,
+                                    page_size, max_pages, n_pool_pages, window, scale, sinks, sink_dtype, d_v, status,
+                                    chunk, n_vh, v_row, maps, out_f32, s);
+    GI_REQUIRE(false, "gi_attention_generic: activation dtype %d", act_dtype);
+}
+
+// Plain grouped-query attention: keys and values of one shape, one softmax per head, no chunks.
 extern "C" int gi_attention_generic(const void* q, const void* k_pool, const void* v_pool, int act_dtype,
                                     const int* block_table, const int* tok_pos, const int* tok_slot,
                                     void* out, int n_tokens, int n_q, int n_kv, int d, int page_size,
                                     int max_pages, int n_pool_pages, int window, float scale, const void* sinks,
                                     int sink_dtype, int d_v, int* status, void* stream) {
-    GI_REQUIRE(n_tokens >= 0 && n_q > 0 && n_kv > 0 && d > 0, "gi_attention_generic: sizes must be positive");
-    GI_REQUIRE(n_q % n_kv == 0, "gi_attention_generic: %d query heads are no multiple of %d key/value heads", n_q, n_kv);
-    GI_REQUIRE(d % 8 == 0 && d <= 1024, "gi_attention_generic: head_dim %d must be a multiple of 8, at most 1024", d);
-    GI_REQUIRE(n_q <= 65535, "gi_attention_generic: %d query heads is beyond 65535", n_q);
     GI_REQUIRE(d_v > 0 && d_v <= d, "gi_attention_generic: %d value columns of rows of %d", d_v, d);
-    GI_REQUIRE(page_size > 0 && max_pages > 0 && window >= 0, "gi_attention_generic: page size, table width and window");
-    if (n_tokens == 0) return 0;
-    cudaStream_t s = (cudaStream_t)stream;
-    if (act_dtype == GI_DTYPE_F32)
-        return launch_generic<float>(q, k_pool, v_pool, block_table, tok_pos, tok_slot, out, n_tokens, n_q, n_kv, d,
-                                     page_size, max_pages, n_pool_pages, window, scale, sinks, sink_dtype, d_v, status, s);
-    if (act_dtype == GI_DTYPE_BF16)
-        return launch_generic<bf16>(q, k_pool, v_pool, block_table, tok_pos, tok_slot, out, n_tokens, n_q, n_kv, d,
-                                    page_size, max_pages, n_pool_pages, window, scale, sinks, sink_dtype, d_v, status, s);
-    GI_REQUIRE(false, "gi_attention_generic: activation dtype %d", act_dtype);
+    return gi_attention_masked(q, k_pool, v_pool, act_dtype, block_table, tok_pos, tok_slot, out, n_tokens, n_q, n_kv, d,
+                               page_size, max_pages, n_pool_pages, window, scale, sinks, sink_dtype, d_v, status, 0, n_kv, d,
+                               1, nullptr, stream);
 }

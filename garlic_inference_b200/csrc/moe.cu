@@ -1,0 +1,212 @@
+// A routed feed-forward: every token runs `top` of `experts` small feed-forwards and sums their results with
+// the router's weights.
+//
+//   gi_router_topk     per token: the `top` largest of its float32 router logits (ties: the lower index), in
+//                      falling order, and the softmax over those chosen logits alone
+//   gi_moe_up          a[t, j, :] = act( W_up[e_tj] x_t )          act: the square of relu (0) or silu (1)
+//   gi_moe_down        y[t, :] = sum_j w_tj W_down[e_tj] a[t, j, :]                  j in the router's order
+//   gi_moe_combine     y[t, :] = sum_j w_tj buf[where[t, j], :]                      the same sum over rows that a
+//                      grouped product wrote expert by expert
+//
+// gi_moe_up and gi_moe_down read only the chosen experts' weights and take the expert of a row from device
+// memory, so a recorded decode step replays them for other tokens.  They are products of one row with a matrix,
+// a warp per row of W, the token's vector in shared memory as float32: the right shape for a handful of tokens.
+// Prompts go expert by expert through the matrix products (parts/moe.py) and gi_moe_combine.  Sums are float32 in a
+// fixed order; a token's result does not depend on the other tokens of the step.
+// NikolayBlagoev/garlic-inference's mixture-of-experts path is a different design (src/models/qwen3/qwen3-moe.cpp).
+#include "common.cuh"
+#include <math.h>
+
+// ------------------------------------------------------------------ router
+__global__ void router_topk_kernel(const float* __restrict__ logits, long long ld, int E, int top,
+                                   int* __restrict__ idx_out, float* __restrict__ w_out, int n_rows) {
+    gi_pdl_start();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (r >= n_rows) return;
+    const float* z = logits + (size_t)r * ld;
+    float first = 0.f, sum = 0.f;
+    float prev_v = INFINITY;
+    int prev_i = -1;
+    for (int j = 0; j < top; ++j) {
+        // the largest logit after (prev_v, prev_i) in the order (value falling, index rising)
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = z[e];
+            const bool after = v < prev_v || (v == prev_v && e > prev_i);
+            if (after && (v > best || (v == best && e < bi))) { best = v; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if (j == 0) first = best;
+        const float p = expf(best - first);
+        sum += p;
+        if (lane == 0) { idx_out[(size_t)r * top + j] = bi; w_out[(size_t)r * top + j] = p; }
+        prev_v = best; prev_i = bi;
+    }
+    __syncwarp();
+    if (lane == 0)
+        for (int j = 0; j < top; ++j) w_out[(size_t)r * top + j] /= sum;
+}
+
+extern "C" int gi_router_topk(const float* logits, long long ld, int E, int top, int* idx_out, float* w_out, int n_rows,
+                              void* stream) {
+    GI_REQUIRE(n_rows >= 0 && E > 0 && top > 0 && top <= E && ld >= E, "gi_router_topk: %d of %d experts", top, E);
+    if (n_rows == 0) return 0;
+    gi_launch(router_topk_kernel, dim3((n_rows + 3) / 4), dim3(128), 0, (cudaStream_t)stream, logits, ld, E, top, idx_out,
+              w_out, n_rows);
+    return gi_check_launch("gi_router_topk");
+}
+
+// ------------------------------------------------------------------ one row times a chosen expert's matrix
+template <typename T> __device__ __forceinline__ float dot_row(const T* __restrict__ w, const float* __restrict__ x, int k, int lane);
+template <> __device__ __forceinline__ float dot_row<float>(const float* __restrict__ w, const float* __restrict__ x, int k, int lane) {
+    float s = 0.f;
+    if (k % 4 == 0 && (uintptr_t)w % 16 == 0) {
+        for (int c = lane * 4; c < k; c += 128) {
+            const float4 v = *reinterpret_cast<const float4*>(w + c);
+            s = fmaf(v.x, x[c], s); s = fmaf(v.y, x[c + 1], s); s = fmaf(v.z, x[c + 2], s); s = fmaf(v.w, x[c + 3], s);
+        }
+    } else {
+        for (int c = lane; c < k; c += 32) s = fmaf(w[c], x[c], s);
+    }
+    return warp_sum(s);
+}
+template <> __device__ __forceinline__ float dot_row<bf16>(const bf16* __restrict__ w, const float* __restrict__ x, int k, int lane) {
+    float s = 0.f;
+    if (k % 8 == 0 && (uintptr_t)w % 16 == 0) {
+        for (int c = lane * 8; c < k; c += 256) {
+            const uint4 v = *reinterpret_cast<const uint4*>(w + c);
+            const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(p2[i]);
+                s = fmaf(f.x, x[c + 2 * i], s);
+                s = fmaf(f.y, x[c + 2 * i + 1], s);
+            }
+        }
+    } else {
+        for (int c = lane; c < k; c += 32) s = fmaf(__bfloat162float(w[c]), x[c], s);
+    }
+    return warp_sum(s);
+}
+
+#define MOE_WARPS 8
+#define MOE_ROWS 32          // rows of W per block
+
+// x [n, ldx] (T), w_up [E, ff, hidden], idx [n, top] -> a [n, top, ff]
+template <typename T>
+__global__ void __launch_bounds__(MOE_WARPS * 32)
+moe_up_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ w_up, const int* __restrict__ idx,
+              T* __restrict__ a, int top, int E, int ff, int hidden, int act) {
+    gi_pdl_start();
+    extern __shared__ float xs[];                   // hidden
+    const int tj = blockIdx.x, t = tj / top;
+    const int e = idx[tj];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) xs[c] = to_f32(x[(size_t)t * ldx + c]);
+    __syncthreads();
+    const bool ok = e >= 0 && e < E;
+    for (int f = blockIdx.y * MOE_ROWS + warp; f < min(ff, (int)(blockIdx.y + 1) * MOE_ROWS); f += MOE_WARPS) {
+        float z = ok ? dot_row<T>(w_up + ((size_t)e * ff + f) * hidden, xs, hidden, lane) : 0.f;
+        if (act == 0) { z = fmaxf(z, 0.f); z = z * z; } else { z = z / (1.f + expf(-z)); }
+        if (lane == 0) a[(size_t)tj * ff + f] = from_f32<T>(z);
+    }
+}
+
+// a [n, top, ff] (T), w_down [E, hidden, ff], idx, wt [n, top] -> y [n, hidden]
+template <typename T>
+__global__ void __launch_bounds__(MOE_WARPS * 32)
+moe_down_kernel(const T* __restrict__ a, const T* __restrict__ w_down, const int* __restrict__ idx,
+                const float* __restrict__ wt, T* __restrict__ y, int top, int E, int ff, int hidden) {
+    gi_pdl_start();
+    extern __shared__ float as[];                   // top * ff
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int c = threadIdx.x; c < top * ff; c += blockDim.x) as[c] = to_f32(a[(size_t)t * top * ff + c]);
+    __syncthreads();
+    for (int c = blockIdx.y * MOE_ROWS + warp; c < min(hidden, (int)(blockIdx.y + 1) * MOE_ROWS); c += MOE_WARPS) {
+        float acc = 0.f;
+        for (int j = 0; j < top; ++j) {
+            const int e = idx[(size_t)t * top + j];
+            if (e < 0 || e >= E) continue;
+            acc = fmaf(wt[(size_t)t * top + j], dot_row<T>(w_down + ((size_t)e * hidden + c) * ff, as + (size_t)j * ff, ff, lane), acc);
+        }
+        if (lane == 0) y[(size_t)t * hidden + c] = from_f32<T>(acc);
+    }
+}
+
+extern "C" int gi_moe_up(const void* x, long long ldx, const void* w_up, const int* idx, void* a, int act_dtype, int n_rows,
+                         int top, int E, int ff, int hidden, int act, void* stream) {
+    GI_REQUIRE(n_rows >= 0 && top > 0 && E > 0 && ff > 0 && hidden > 0 && ldx >= hidden, "gi_moe_up: sizes");
+    GI_REQUIRE((ff + MOE_ROWS - 1) / MOE_ROWS <= 65535 && (act == 0 || act == 1), "gi_moe_up: %d rows per expert, activation %d", ff, act);
+    if (n_rows == 0) return 0;
+    const size_t smem = (size_t)hidden * sizeof(float);
+    dim3 grid(n_rows * top, (ff + MOE_ROWS - 1) / MOE_ROWS);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (act_dtype == GI_DTYPE_F32) {
+        if (smem > 48 * 1024) { int rc = gi_reserve_smem((const void*)moe_up_kernel<float>, smem, "gi_moe_up"); if (rc) return rc; }
+        gi_launch(moe_up_kernel<float>, grid, dim3(MOE_WARPS * 32), smem, s, (const float*)x, ldx, (const float*)w_up, idx, (float*)a, top, E, ff, hidden, act);
+    } else if (act_dtype == GI_DTYPE_BF16) {
+        if (smem > 48 * 1024) { int rc = gi_reserve_smem((const void*)moe_up_kernel<bf16>, smem, "gi_moe_up"); if (rc) return rc; }
+        gi_launch(moe_up_kernel<bf16>, grid, dim3(MOE_WARPS * 32), smem, s, (const bf16*)x, ldx, (const bf16*)w_up, idx, (bf16*)a, top, E, ff, hidden, act);
+    } else {
+        GI_REQUIRE(false, "gi_moe_up: activation dtype %d", act_dtype);
+    }
+    return gi_check_launch("gi_moe_up");
+}
+
+extern "C" int gi_moe_down(const void* a, const void* w_down, const int* idx, const float* wt, void* y, int act_dtype,
+                           int n_rows, int top, int E, int ff, int hidden, void* stream) {
+    GI_REQUIRE(n_rows >= 0 && top > 0 && E > 0 && ff > 0 && hidden > 0, "gi_moe_down: sizes");
+    GI_REQUIRE((hidden + MOE_ROWS - 1) / MOE_ROWS <= 65535, "gi_moe_down: %d output channels", hidden);
+    if (n_rows == 0) return 0;
+    const size_t smem = (size_t)top * ff * sizeof(float);
+    GI_REQUIRE(smem <= 200 * 1024, "gi_moe_down: %d chosen experts of %d do not fit shared memory", top, ff);
+    dim3 grid(n_rows, (hidden + MOE_ROWS - 1) / MOE_ROWS);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (act_dtype == GI_DTYPE_F32) {
+        if (smem > 48 * 1024) { int rc = gi_reserve_smem((const void*)moe_down_kernel<float>, smem, "gi_moe_down"); if (rc) return rc; }
+        gi_launch(moe_down_kernel<float>, grid, dim3(MOE_WARPS * 32), smem, s, (const float*)a, (const float*)w_down, idx, wt, (float*)y, top, E, ff, hidden);
+    } else if (act_dtype == GI_DTYPE_BF16) {
+        if (smem > 48 * 1024) { int rc = gi_reserve_smem((const void*)moe_down_kernel<bf16>, smem, "gi_moe_down"); if (rc) return rc; }
+        gi_launch(moe_down_kernel<bf16>, grid, dim3(MOE_WARPS * 32), smem, s, (const bf16*)a, (const bf16*)w_down, idx, wt, (bf16*)y, top, E, ff, hidden);
+    } else {
+        GI_REQUIRE(false, "gi_moe_down: activation dtype %d", act_dtype);
+    }
+    return gi_check_launch("gi_moe_down");
+}
+
+// ------------------------------------------------------------------ the weighted sum over rows written expert by expert
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ buf, const int* __restrict__ where, const float* __restrict__ wt,
+                                   T* __restrict__ y, int top, int hidden) {
+    gi_pdl_start();
+    const size_t t = blockIdx.x;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < hidden; c += gridDim.y * blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < top; ++j)
+            acc = fmaf(wt[t * top + j], to_f32(buf[(size_t)where[t * top + j] * hidden + c]), acc);
+        y[t * hidden + c] = from_f32<T>(acc);
+    }
+}
+
+extern "C" int gi_moe_combine(const void* buf, const int* where, const float* wt, void* y, int act_dtype, int n_rows,
+                              int top, int hidden, void* stream) {
+    GI_REQUIRE(n_rows >= 0 && top > 0 && hidden > 0, "gi_moe_combine: sizes");
+    if (n_rows == 0) return 0;
+    dim3 grid(n_rows, (hidden + 1023) / 1024);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (act_dtype == GI_DTYPE_F32)
+        gi_launch(moe_combine_kernel<float>, grid, dim3(256), 0, s, (const float*)buf, where, wt, (float*)y, top, hidden);
+    else if (act_dtype == GI_DTYPE_BF16)
+        gi_launch(moe_combine_kernel<bf16>, grid, dim3(256), 0, s, (const bf16*)buf, where, wt, (bf16*)y, top, hidden);
+    else
+        GI_REQUIRE(false, "gi_moe_combine: activation dtype %d", act_dtype);
+    return gi_check_launch("gi_moe_combine");
+}

@@ -8,7 +8,9 @@
 //                           projections): linear attention with one fixed decay per head
 //   gi_delta_scan           S <- g_t S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t
 //                           with q, k made unit vectors per head (q also times dim^-1/2),
-//                           g_t = exp(-exp(A_h) softplus(a_t + dt_h)),  beta_t = sigmoid(b_t): the gated delta rule
+//                           g_t = exp(-exp(A_h) softplus(a_t + dt_h)),  beta_t = sigmoid(b_t): the gated delta rule;
+//                           the decay is one number per head, or one per head and key channel (row c of a head's
+//                           state times g_t[c])
 //
 // A scan block owns one (sequence, head, slice of 32 value columns) and walks the sequence's tokens of this
 // step in order, so prompts, portions of prompts and single tokens run the same instructions in the same
@@ -41,7 +43,7 @@ __device__ __forceinline__ int rows_before(const int* __restrict__ tok_slot, int
 template <typename T>
 __global__ void causal_conv_silu_kernel(const T* __restrict__ x, long long ldx, int C, const void* __restrict__ taps,
                                         int taps_dtype, int K, const float* __restrict__ state, long long state_stride,
-                                        const int* __restrict__ tok_slot, float* __restrict__ out) {
+                                        const int* __restrict__ tok_slot, float* __restrict__ out, int act) {
     gi_pdl_start();
     const int r = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
@@ -55,7 +57,7 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ x, long long ldx, 
         else if (slot >= 0) xv = state[(size_t)slot * state_stride + (size_t)(K - 1 + have - j) * C + c];
         acc = fmaf(load_w(taps, taps_dtype, c * K + (K - 1 - j)), xv, acc);
     }
-    out[(size_t)r * C + c] = rc_silu(acc);
+    out[(size_t)r * C + c] = act ? rc_silu(acc) : acc;
 }
 
 template <typename T>
@@ -78,9 +80,10 @@ __global__ void conv_state_update_kernel(const T* __restrict__ x, long long ldx,
     for (int m = 0; m < K - 1; ++m) st[(size_t)m * C + c] = vals[m];
 }
 
-extern "C" int gi_causal_conv_silu(const void* x, long long ldx, int act_dtype, int C, const void* taps, int taps_dtype,
-                                   int K, float* state, long long state_stride, const int* tok_slot, float* out,
-                                   int n_rows, int update_state, void* stream) {
+// `act` 1: silu of the filter's sum; 0: the sum itself.
+extern "C" int gi_causal_conv(const void* x, long long ldx, int act_dtype, int C, const void* taps, int taps_dtype,
+                              int K, float* state, long long state_stride, const int* tok_slot, float* out,
+                              int n_rows, int update_state, int act, void* stream) {
     GI_REQUIRE(n_rows >= 0 && C > 0 && K >= 1 && K <= CONV_MAX_TAPS, "gi_causal_conv_silu: %d channels, %d taps (1 to %d)",
                C, K, CONV_MAX_TAPS);
     GI_REQUIRE(ldx >= C && state_stride >= (long long)(K - 1) * C, "gi_causal_conv_silu: strides shorter than the rows");
@@ -89,15 +92,22 @@ extern "C" int gi_causal_conv_silu(const void* x, long long ldx, int act_dtype, 
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_rows, (C + 127) / 128);
     if (act_dtype == GI_DTYPE_F32) {
-        if (!update_state) gi_launch(causal_conv_silu_kernel<float>, grid, dim3(128), 0, s, (const float*)x, ldx, C, taps, taps_dtype, K, (const float*)state, state_stride, tok_slot, out);
+        if (!update_state) gi_launch(causal_conv_silu_kernel<float>, grid, dim3(128), 0, s, (const float*)x, ldx, C, taps, taps_dtype, K, (const float*)state, state_stride, tok_slot, out, act);
         else if (K > 1) gi_launch(conv_state_update_kernel<float>, grid, dim3(128), 0, s, (const float*)x, ldx, C, K, state, state_stride, tok_slot, n_rows);
     } else if (act_dtype == GI_DTYPE_BF16) {
-        if (!update_state) gi_launch(causal_conv_silu_kernel<bf16>, grid, dim3(128), 0, s, (const bf16*)x, ldx, C, taps, taps_dtype, K, (const float*)state, state_stride, tok_slot, out);
+        if (!update_state) gi_launch(causal_conv_silu_kernel<bf16>, grid, dim3(128), 0, s, (const bf16*)x, ldx, C, taps, taps_dtype, K, (const float*)state, state_stride, tok_slot, out, act);
         else if (K > 1) gi_launch(conv_state_update_kernel<bf16>, grid, dim3(128), 0, s, (const bf16*)x, ldx, C, K, state, state_stride, tok_slot, n_rows);
     } else {
         GI_REQUIRE(false, "gi_causal_conv_silu: activation dtype %d", act_dtype);
     }
     return gi_check_launch("gi_causal_conv_silu");
+}
+
+extern "C" int gi_causal_conv_silu(const void* x, long long ldx, int act_dtype, int C, const void* taps, int taps_dtype,
+                                   int K, float* state, long long state_stride, const int* tok_slot, float* out,
+                                   int n_rows, int update_state, void* stream) {
+    return gi_causal_conv(x, ldx, act_dtype, C, taps, taps_dtype, K, state, state_stride, tok_slot, out, n_rows,
+                          update_state, 1, stream);
 }
 
 // ------------------------------------------------------------------ scans
@@ -263,20 +273,26 @@ decay_scan_kernel(const T* __restrict__ qkv, long long ld, int q_off, int k_off,
 // head h at v_off + h dv.  ab: float32 [n, ldab]: beta's logit of head h at column b_off + h, the decay's at
 // a_off + h (float32 whatever the activation type is: the decay's logit is multiplied by exp(A_h) and goes
 // through two exponentials, which would magnify a 16-bit rounding).
-template <typename T, int R, int P>
+// CH = 1: a decay per head and key channel.  The logits are then [n, H d] (column a_off + h d + c), dt_bias has
+// H d elements, and row c of a head's state is multiplied by g[c]; chunks are shorter so that the decays of a
+// chunk fit shared memory beside its keys.
+#define SCAN_TC_CH(DP) ((DP) <= 64 ? 32 : ((DP) <= 128 ? 16 : 8))
+template <typename T, int R, int P, int CH>
 __global__ void __launch_bounds__(SCAN_VS * P)
 delta_scan_kernel(const float* __restrict__ qkv, long long ldq, int q_off, int k_off, int v_off,
                   const float* __restrict__ ab, long long ldab, int b_off, int a_off,
+                  const float* __restrict__ al, long long ldal,
                   const void* __restrict__ A_log, const void* __restrict__ dt_bias, int p_dtype,
                   float* __restrict__ state, long long state_stride, const int* __restrict__ spans,
                   const int* __restrict__ tok_slot, float* __restrict__ out, int H, int Hk, int d, int dv,
                   float unit_eps, float q_scale, int vec) {
     gi_pdl_start();
     constexpr int DP = R * P;
-    constexpr int TC = SCAN_TC(DP);
+    constexpr int TC = CH ? SCAN_TC_CH(DP) : SCAN_TC(DP);
     constexpr int SCAN_THREADS = SCAN_VS * P;
     __shared__ __align__(16) float q_s[TC][DP];
     __shared__ __align__(16) float k_s[TC][DP];
+    __shared__ __align__(16) float gc_s[CH ? TC : 1][CH ? DP : 4];
     __shared__ float v_s[TC][SCAN_VS];
     __shared__ float o_s[TC][SCAN_VS];
     __shared__ float g_s[TC], b_s[TC];
@@ -292,7 +308,7 @@ delta_scan_kernel(const float* __restrict__ qkv, long long ldq, int q_off, int k
             if (live && part == 0) out[(size_t)(start + t) * H * dv + h * dv + v] = 0.f;
         return;
     }
-    const float rate = expf(load_w(A_log, p_dtype, h)), dt = load_w(dt_bias, p_dtype, h);
+    const float rate = expf(load_w(A_log, p_dtype, h)), dt = CH ? 0.f : load_w(dt_bias, p_dtype, h);
     float* st = state + (size_t)slot * state_stride + ((size_t)h * dv + (live ? v : 0)) * DP;
     float S[R];
     if (live) scan_load_state<R, P>(S, st, part);
@@ -337,9 +353,14 @@ delta_scan_kernel(const float* __restrict__ qkv, long long ldq, int q_off, int k
                 }
             }
             v_s[t][lane] = v0 + lane < dv ? row[v_off + h * dv + v0 + lane] : 0.f;
+            const float* abr = ab + (size_t)(start + t0 + t) * ldab;
+            const float* alr = al + (size_t)(start + t0 + t) * ldal;
+            if (CH) {
+                for (int c = lane; c < DP; c += 32)
+                    gc_s[t][c] = c < d ? expf(-rate * rc_softplus(alr[a_off + h * d + c] + load_w(dt_bias, p_dtype, h * d + c))) : 1.f;
+            }
             if (lane == 0) {
-                const float* abr = ab + (size_t)(start + t0 + t) * ldab;
-                g_s[t] = expf(-rate * rc_softplus(abr[a_off + h] + dt));
+                if (!CH) g_s[t] = expf(-rate * rc_softplus(alr[a_off + h] + dt));
                 b_s[t] = rc_sigmoid(abr[b_off + h]);
             }
         }
@@ -352,15 +373,17 @@ delta_scan_kernel(const float* __restrict__ qkv, long long ldq, int q_off, int k
         }
         __syncthreads();
         for (int t = 0; t < tc; ++t) {
-            const float g = g_s[t];
+            const float g = CH ? 1.f : g_s[t];
             float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;     // four chains instead of one of R dependent steps
 #pragma unroll
             for (int i = 0; i < R / 4; ++i) {
                 const float4 kk = *reinterpret_cast<const float4*>(&k_s[t][KEY_OF(i, part)]);
-                S[4 * i] *= g;      r0 = fmaf(S[4 * i], kk.x, r0);
-                S[4 * i + 1] *= g;  r1 = fmaf(S[4 * i + 1], kk.y, r1);
-                S[4 * i + 2] *= g;  r2 = fmaf(S[4 * i + 2], kk.z, r2);
-                S[4 * i + 3] *= g;  r3 = fmaf(S[4 * i + 3], kk.w, r3);
+                float4 gg = make_float4(g, g, g, g);
+                if (CH) gg = *reinterpret_cast<const float4*>(&gc_s[t][KEY_OF(i, part)]);
+                S[4 * i] *= gg.x;      r0 = fmaf(S[4 * i], kk.x, r0);
+                S[4 * i + 1] *= gg.y;  r1 = fmaf(S[4 * i + 1], kk.y, r1);
+                S[4 * i + 2] *= gg.z;  r2 = fmaf(S[4 * i + 2], kk.z, r2);
+                S[4 * i + 3] *= gg.w;  r3 = fmaf(S[4 * i + 3], kk.w, r3);
             }
             const float r = part_sum<P>((r0 + r1) + (r2 + r3));
             const float u = b_s[t] * (v_s[t][vl] - r);
@@ -401,14 +424,17 @@ extern "C" long long gi_scan_state_floats(int d, int dv) {
 
 // (registers, lanes per column) by padded key dimension: 16 -> (4, 4), 32 -> (8, 4), 64 -> (8, 8), 128 -> (16, 8),
 // 256 -> (32, 8)
-#define SCAN_DISPATCH(KERNEL, TT, ...)                                                                   \
+#define SCAN_DISPATCH_X(KERNEL, TT, X, ...)                                                              \
     switch (DP) {                                                                                        \
-        case 16:  gi_launch(KERNEL<TT, 4, 4>, grid, dim3(SCAN_VS * 4), 0, s, __VA_ARGS__); break;        \
-        case 32:  gi_launch(KERNEL<TT, 8, 4>, grid, dim3(SCAN_VS * 4), 0, s, __VA_ARGS__); break;        \
-        case 64:  gi_launch(KERNEL<TT, 8, 8>, grid, dim3(SCAN_VS * 8), 0, s, __VA_ARGS__); break;        \
-        case 128: gi_launch(KERNEL<TT, 16, 8>, grid, dim3(SCAN_VS * 8), 0, s, __VA_ARGS__); break;       \
-        default:  gi_launch(KERNEL<TT, 32, 8>, grid, dim3(SCAN_VS * 8), 0, s, __VA_ARGS__); break;       \
+        case 16:  gi_launch(KERNEL<TT, 4, 4 X>, grid, dim3(SCAN_VS * 4), 0, s, __VA_ARGS__); break;      \
+        case 32:  gi_launch(KERNEL<TT, 8, 4 X>, grid, dim3(SCAN_VS * 4), 0, s, __VA_ARGS__); break;      \
+        case 64:  gi_launch(KERNEL<TT, 8, 8 X>, grid, dim3(SCAN_VS * 8), 0, s, __VA_ARGS__); break;      \
+        case 128: gi_launch(KERNEL<TT, 16, 8 X>, grid, dim3(SCAN_VS * 8), 0, s, __VA_ARGS__); break;     \
+        default:  gi_launch(KERNEL<TT, 32, 8 X>, grid, dim3(SCAN_VS * 8), 0, s, __VA_ARGS__); break;     \
     }
+#define SCAN_NOTHING
+#define SCAN_COMMA(v) , v
+#define SCAN_DISPATCH(KERNEL, TT, ...) SCAN_DISPATCH_X(KERNEL, TT, SCAN_NOTHING, __VA_ARGS__)
 
 extern "C" int gi_decay_scan(const void* qkv, long long ld, int act_dtype, int q_off, int k_off, int v_off,
                              const float* decay, float* state, long long state_stride, const int* spans,
@@ -434,10 +460,11 @@ extern "C" int gi_decay_scan(const void* qkv, long long ld, int act_dtype, int q
 }
 
 extern "C" int gi_delta_scan(const float* qkv, long long ldq, int q_off, int k_off, int v_off, const float* ab,
-                             long long ldab, int b_off, int a_off, const void* A_log, const void* dt_bias,
+                             long long ldab, int b_off, int a_off, const float* a_sep, long long lda_sep,
+                             const void* A_log, const void* dt_bias,
                              int p_dtype, float* state, long long state_stride, const int* spans, const int* tok_slot,
                              float* out, int n_seq, int H, int Hk, int d, int dv, float unit_eps, float q_scale,
-                             void* stream) {
+                             int channel_decay, void* stream) {
     const int DP = scan_padded(d);
     GI_REQUIRE(n_seq >= 0 && H > 0 && Hk > 0 && H % Hk == 0 && d > 0 && dv > 0 && DP > 0,
                "gi_delta_scan: %d heads on %d key heads, key dimension %d (at most 256)", H, Hk, d);
@@ -448,6 +475,13 @@ extern "C" int gi_delta_scan(const float* qkv, long long ldq, int q_off, int k_o
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_seq, H, (dv + SCAN_VS - 1) / SCAN_VS);
     const int vec = d % 4 == 0 && ldq % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 && (uintptr_t)qkv % 16 == 0;
-    SCAN_DISPATCH(delta_scan_kernel, float, qkv, ldq, q_off, k_off, v_off, ab, ldab, b_off, a_off, A_log, dt_bias, p_dtype, state, state_stride, spans, tok_slot, out, H, Hk, d, dv, unit_eps, q_scale, vec)
+    // the decay's logits: columns of `ab`, or a matrix of their own
+    const float* al = a_sep ? a_sep : ab;
+    const long long ldal = a_sep ? lda_sep : ldab;
+    if (channel_decay) {
+        SCAN_DISPATCH_X(delta_scan_kernel, float, SCAN_COMMA(1), qkv, ldq, q_off, k_off, v_off, ab, ldab, b_off, a_off, al, ldal, A_log, dt_bias, p_dtype, state, state_stride, spans, tok_slot, out, H, Hk, d, dv, unit_eps, q_scale, vec)
+    } else {
+        SCAN_DISPATCH_X(delta_scan_kernel, float, SCAN_COMMA(0), qkv, ldq, q_off, k_off, v_off, ab, ldab, b_off, a_off, al, ldal, A_log, dt_bias, p_dtype, state, state_stride, spans, tok_slot, out, H, Hk, d, dv, unit_eps, q_scale, vec)
+    }
     return gi_check_launch("gi_delta_scan");
 }

@@ -11,10 +11,10 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------- embedding
-// out[t, :] = table[ids[t], :] as float32.  An id outside [0, vocab) writes zeros.
+// out[t, :] = table[ids[t], :] * scale as float32 (scale 1 for models without one).  An id outside [0, vocab) writes zeros.
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
-                                 float* __restrict__ out, int vocab, int hidden) {
+                                 float* __restrict__ out, int vocab, int hidden, float scale) {
     gi_pdl_start();
     const int t = blockIdx.x;
     const int id = ids[t];
@@ -24,19 +24,19 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
         return;
     }
     const T* src = table + (size_t)id * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32(src[i]);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32(src[i]) * scale;
 }
 
 extern "C" int gi_embedding(const int* ids, const void* table, int table_dtype, float* out,
-                            int n_tokens, int vocab, int hidden, void* stream) {
+                            int n_tokens, int vocab, int hidden, float scale, void* stream) {
     GI_REQUIRE(n_tokens >= 0 && vocab > 0 && hidden > 0, "gi_embedding: sizes must be positive");
     if (n_tokens == 0) return 0;
     const int threads = hidden >= 1024 ? 256 : 128;
     cudaStream_t s = (cudaStream_t)stream;
     if (table_dtype == GI_DTYPE_F32)
-        gi_launch(embedding_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, ids, (const float*)table, out, vocab, hidden);
+        gi_launch(embedding_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, ids, (const float*)table, out, vocab, hidden, scale);
     else if (table_dtype == GI_DTYPE_BF16)
-        gi_launch(embedding_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, ids, (const bf16*)table, out, vocab, hidden);
+        gi_launch(embedding_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, ids, (const bf16*)table, out, vocab, hidden, scale);
     else
         GI_REQUIRE(false, "gi_embedding: table dtype %d is neither float32 nor bfloat16", table_dtype);
     return gi_check_launch("gi_embedding");

@@ -70,8 +70,10 @@ class LanguageModel:
             torch.cuda.set_device(dev)
         require_gpu()
         config = load_config(model_dir)
-        plan = config.plan()
         ckpt = Checkpoint(model_dir)
+        if hasattr(config, "with_shapes"):          # sizes that no key gives and only the tensors have
+            config = config.with_shapes({n: tuple(ckpt.shape(n)) for n in ckpt.names()})
+        plan = config.plan()
         ckpt.check(wanted_tensors(plan))
         model = DecoderModel(plan, ckpt, Runtime(engine_dtype(dtype), dev))
         stop = ()

@@ -106,10 +106,23 @@ class DecoderModel:
 
     def cache_requirements(self) -> list:
         """What each cache entry has to hold; entries shared by several runs must agree."""
+        from ..cache import EntryRequirement, split_requirement
         reqs: list = [None] * self.plan.n_cache_entries()
         written = [False] * len(reqs)
         for e in self.schedule:
             req = self.blocks[e.layer].cache_requirement()
+            if e.kv_cache is not None:
+                # the run reads another entry's keys and values: they must have the shape this layer asks for, and
+                # the entry of its own keeps the layer's state alone
+                kv_req, state_req = split_requirement(req)
+                src_kv = split_requirement(reqs[e.kv_cache])[0] if 0 <= e.kv_cache < len(reqs) else None
+                if not written[e.kv_cache] or src_kv is None:
+                    raise ValueError(f"the schedule reads the keys and values of cache entry {e.kv_cache} before any "
+                                     "layer wrote them")
+                if kv_req != src_kv:
+                    raise ValueError(f"a layer reads the keys and values of cache entry {e.kv_cache} ({src_kv}) but "
+                                     f"asks for {kv_req}")
+                req = EntryRequirement(None, state_req) if state_req is not None else None
             if reqs[e.cache] is not None and reqs[e.cache] != req:
                 raise ValueError(f"cache entry {e.cache} is used by layers with different needs: "
                                  f"{reqs[e.cache]} and {req}")
@@ -124,7 +137,7 @@ class DecoderModel:
         ({name: numpy array}); the engine copies them with the step's own arrays."""
         out: dict = {}
         for e in self.schedule:
-            for name, make in self.blocks[e.layer].step_arrays(shape, cache.view(e.cache)).items():
+            for name, make in self.blocks[e.layer].step_arrays(shape, cache.view(e.cache, e.kv_cache)).items():
                 if name not in out:
                     out[name] = make()
         return out
@@ -133,15 +146,18 @@ class DecoderModel:
         """Run the step's tokens through every scheduled layer; float32 logits [n_wanted, vocab] at
         `want_rows` (int32 row indices), or None when nothing is wanted."""
         ctx.residual_act = None                      # a context may be run again (recording a decode step)
+        ctx.delta_scale = None
         residual = self.embedding.step(ctx)
         for pos in self.positions.values():
             pos.on_embedding(residual, ctx)
         delta = None
         for e in self.schedule:
-            delta = self.blocks[e.layer].step(delta, residual, ctx, cache.view(e.cache), e.writes_cache)
+            delta = self.blocks[e.layer].step(delta, residual, ctx, cache.view(e.cache, e.kv_cache),
+                                              e.writes_cache and e.kv_cache is None)
         if want_rows is None or want_rows.numel() == 0:
             return None
-        normed = self.final_norm.add_norm(delta, residual, rows=want_rows)
+        scaled = {"delta_scale": ctx.delta_scale} if ctx.delta_scale is not None and delta is not None else {}
+        normed = self.final_norm.add_norm(delta, residual, rows=want_rows, **scaled)
         return self.head.step(normed)
 
     def weight_bytes(self) -> int:

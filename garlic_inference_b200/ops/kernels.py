@@ -49,8 +49,8 @@ def set_dependent_launch(on: bool) -> None:
     require_gpu().gi_set_pdl(1 if on else 0)
 
 
-def embedding(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """float32 rows of `table` for int32 `ids`: the start of the residual stream."""
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None, scale: float = 1.0) -> torch.Tensor:
+    """float32 rows of `table` for int32 `ids`, times `scale`: the start of the residual stream."""
     l = require_gpu()
     _dense(ids, "ids", torch.int32)
     _dense(table, "table")
@@ -58,7 +58,7 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor
     if out is None:
         out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
     _dense(out, "out", torch.float32)
-    check(l.gi_embedding(_ptr(ids), _ptr(table), code(table.dtype), _ptr(out), n, vocab, hidden, _stream()), l)
+    check(l.gi_embedding(_ptr(ids), _ptr(table), code(table.dtype), _ptr(out), n, vocab, hidden, float(scale), _stream()), l)
     return out
 
 
@@ -205,6 +205,200 @@ def attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
     return out
 
 
+def attention_masked(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
+                     tok_pos: torch.Tensor, tok_slot: torch.Tensor, scale: float, status: torch.Tensor, window: int = 0,
+                     chunk: int = 0, maps: int = 1, out_float32: bool = False) -> torch.Tensor:
+    """Exact-order attention of q [n, rows, d] over keys [pages, key heads, page, d] and values [pages, value
+    heads, page, dv] of their own shape.  `chunk` > 0: a query sees the keys of its own chunk of positions only
+    (chunks counted from position 0).  `maps` > 1: the rows of a token are [head][map] and the key heads [key
+    head][map]; every map is a softmax of its own over the head's values.  Returns [n, rows * dv], float32 when
+    asked, else q's type."""
+    l = require_gpu()
+    _dense(q, "q"), _dense(k_pool, "k_pool", q.dtype), _dense(v_pool, "v_pool", q.dtype)
+    n, n_q, d = q.shape
+    n_pages, n_kv, page_size, pool_d = k_pool.shape
+    v_pages, n_vh, v_page, dv = v_pool.shape
+    if pool_d != d or (v_pages, v_page) != (n_pages, page_size):
+        raise KernelError(f"cache pools {tuple(k_pool.shape)} / {tuple(v_pool.shape)} do not fit queries of {d}")
+    for t, name in ((tok_pos, "tok_pos"), (tok_slot, "tok_slot"), (block_table, "block_table"), (status, "status")):
+        _dense(t, name, torch.int32)
+    out = torch.empty((n, n_q * dv), dtype=torch.float32 if out_float32 else q.dtype, device=q.device)
+    check(l.gi_attention_masked(_ptr(q), _ptr(k_pool), _ptr(v_pool), code(q.dtype), _ptr(block_table), _ptr(tok_pos),
+                                _ptr(tok_slot), None if out_float32 else _ptr(out), n, n_q, n_kv, d, page_size,
+                                block_table.shape[1], n_pages, int(window or 0), float(scale), None, F32, dv,
+                                _ptr(status), int(chunk or 0), n_vh, dv, int(maps), _ptr(out) if out_float32 else None,
+                                _stream()), l)
+    return out
+
+
+def attn_prepare(src: torch.Tensor, q_off: int, k_off: int, v_off: int, freq: Optional[torch.Tensor], n_rot: int,
+                 half_layout: bool, tok_pos: torch.Tensor, tok_slot: torch.Tensor, block_table: Optional[torch.Tensor],
+                 k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor], n_q_rows: int, d: int,
+                 act_dtype: torch.dtype, status: torch.Tensor, append: bool = True) -> torch.Tensor:
+    """Between projections (or convolutions) and attention: the queries of `src` [n, >= columns] at `q_off` come
+    back as [n, n_q_rows, d] in `act_dtype`, their first `n_rot` dimensions turned by position x `freq`; with
+    `k_off` >= 0 the keys (turned alike) and values at `k_off` / `v_off` go into the token's cache page."""
+    l = require_gpu()
+    _rows(src, "src")
+    n = src.shape[0]
+    for t, name in ((tok_pos, "tok_pos"), (tok_slot, "tok_slot"), (status, "status")):
+        _dense(t, name, torch.int32)
+    if n_rot:
+        _dense(freq, "freq", torch.float32)
+        if freq.numel() * 2 != n_rot:
+            raise KernelError(f"{freq.numel()} frequencies for {n_rot} rotated dimensions")
+    n_kh = n_vh = dv = page_size = max_pages = n_pages = 0
+    if k_off >= 0:
+        _dense(k_pool, "k_pool", act_dtype), _dense(v_pool, "v_pool", act_dtype), _dense(block_table, "block_table", torch.int32)
+        n_pages, n_kh, page_size, pool_d = k_pool.shape
+        _, n_vh, _, dv = v_pool.shape
+        max_pages = block_table.shape[1]
+        if pool_d != d:
+            raise KernelError(f"key pool rows of {pool_d} for heads of {d}")
+    q_out = torch.empty((n, n_q_rows, d), dtype=act_dtype, device=src.device)
+    check(l.gi_attn_prepare(_ptr(src), code(src.dtype), src.stride(0), q_off, k_off, v_off, _ptr(freq) if n_rot else None,
+                            n_rot, int(half_layout), _ptr(tok_pos), _ptr(tok_slot), _ptr(block_table) if k_off >= 0 else None,
+                            _ptr(k_pool) if k_off >= 0 else None, _ptr(v_pool) if k_off >= 0 else None, _ptr(q_out),
+                            code(act_dtype), n, n_q_rows, n_kh, n_vh, d, max(dv, 1), page_size, max_pages, n_pages,
+                            int(append), _ptr(status), _stream()), l)
+    return q_out
+
+
+def attn_finish(att: torch.Tensor, heads: int, maps: int, lam: Optional[torch.Tensor], norm_eps: Optional[float],
+                mul: float, gate: Optional[torch.Tensor], act_dtype: torch.dtype,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """att [n, heads * maps * dv] -> [n, heads * dv] in `act_dtype`: a_1 - lam a_2 for two maps, divided by its root
+    mean square per head when `norm_eps` is given, times `mul`, times sigmoid(gate[:, head]).  `out` may be columns
+    of a wider matrix."""
+    l = require_gpu()
+    _dense(att, "att")
+    n = att.shape[0]
+    dv = att.shape[1] // (heads * maps)
+    if gate is not None:
+        _rows(gate, "gate", act_dtype)
+    if lam is not None:
+        _dense(lam, "lam", torch.float32)
+    if out is None:
+        out = torch.empty((n, heads * dv), dtype=act_dtype, device=att.device)
+    _rows(out, "out", act_dtype)
+    check(l.gi_attn_finish(_ptr(att), code(att.dtype), maps, _ptr(lam), float(norm_eps or 0.0), int(norm_eps is not None),
+                           float(mul), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(out), out.stride(0),
+                           code(act_dtype), n, heads, dv, _stream()), l)
+    return out
+
+
+def add_dyt(delta: Optional[torch.Tensor], delta_scale: Optional[torch.Tensor], residual: torch.Tensor,
+            weight: torch.Tensor, bias: torch.Tensor, alpha: torch.Tensor, act_dtype: torch.dtype,
+            rows: Optional[torch.Tensor] = None, write_residual: bool = True) -> torch.Tensor:
+    """tanh(alpha s) * weight + bias for s = residual (+ delta * delta_scale), in `act_dtype`; the float32 sum goes
+    back into `residual` unless `rows` (int32) picks rows or `write_residual` is False."""
+    l = require_gpu()
+    _dense(residual, "residual", torch.float32), _dense(weight, "weight"), _dense(bias, "bias", weight.dtype)
+    _dense(alpha, "alpha", weight.dtype)
+    dim = residual.shape[-1]
+    if weight.numel() != dim or bias.numel() != dim or alpha.numel() != 1:
+        raise KernelError(f"norm tensors of {weight.numel()}, {bias.numel()} and {alpha.numel()} elements for rows of {dim}")
+    if delta is not None:
+        _dense(delta, "delta", act_dtype)
+        if delta.shape != residual.shape:
+            raise KernelError(f"delta {tuple(delta.shape)} and residual {tuple(residual.shape)} differ")
+    if delta_scale is not None and _dense(delta_scale, "delta_scale").numel() != dim:
+        raise KernelError(f"a factor per channel has {delta_scale.numel()} elements for rows of {dim}")
+    if rows is not None:
+        _dense(rows, "rows", torch.int32)
+        n_rows, write_residual = rows.numel(), False
+    else:
+        n_rows = residual.numel() // dim
+    out = torch.empty((n_rows, dim), dtype=act_dtype, device=residual.device)
+    check(l.gi_add_dyt(_ptr(delta), _ptr(delta_scale), code(delta_scale.dtype) if delta_scale is not None else F32,
+                       _ptr(residual), _ptr(weight), _ptr(bias), _ptr(alpha), code(weight.dtype), _ptr(out),
+                       code(act_dtype), _ptr(rows), n_rows, dim, int(write_residual and delta is not None), _stream()), l)
+    return out
+
+
+def residual_add_scaled(delta: torch.Tensor, delta_scale: Optional[torch.Tensor], residual: torch.Tensor) -> None:
+    """residual += delta * delta_scale (a factor per channel; None: 1)."""
+    l = require_gpu()
+    _dense(delta, "delta"), _dense(residual, "residual", torch.float32)
+    if delta.shape != residual.shape:
+        raise KernelError(f"delta {tuple(delta.shape)} and residual {tuple(residual.shape)} differ")
+    n, dim = residual.shape
+    check(l.gi_residual_add_scaled(_ptr(delta), code(delta.dtype), _ptr(delta_scale),
+                                   code(delta_scale.dtype) if delta_scale is not None else F32, _ptr(residual), n, dim,
+                                   _stream()), l)
+
+
+def glu(gate_up: torch.Tensor, activation: str) -> torch.Tensor:
+    """act(gate) * up for rows [gate | up]; activation "silu" or "gelu_tanh"."""
+    l = require_gpu()
+    _rows(gate_up, "gate_up")
+    n, two_i = gate_up.shape
+    out = torch.empty((n, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    check(l.gi_glu(_ptr(gate_up), gate_up.stride(0), _ptr(out), code(gate_up.dtype), n, two_i // 2,
+                   {"silu": 0, "gelu_tanh": 1}[activation], _stream()), l)
+    return out
+
+
+def relu_squared(z: torch.Tensor) -> torch.Tensor:
+    l = require_gpu()
+    _dense(z, "z")
+    out = torch.empty_like(z)
+    check(l.gi_relu_squared(_ptr(z), _ptr(out), code(z.dtype), z.numel(), _stream()), l)
+    return out
+
+
+def scaled_sum(a: torch.Tensor, ca: float, b: torch.Tensor, cb: float) -> torch.Tensor:
+    """a * ca + b * cb, float32 inside."""
+    l = require_gpu()
+    _dense(a, "a"), _dense(b, "b", a.dtype)
+    if a.shape != b.shape:
+        raise KernelError(f"{tuple(a.shape)} and {tuple(b.shape)} differ")
+    out = torch.empty_like(a)
+    check(l.gi_scaled_sum(_ptr(a), float(ca), _ptr(b), float(cb), _ptr(out), code(a.dtype), a.numel(), _stream()), l)
+    return out
+
+
+def router_topk(logits: torch.Tensor, top: int):
+    """(chosen experts int32 [n, top] in falling order of their logits, softmax over the chosen logits float32)."""
+    l = require_gpu()
+    _rows(logits, "logits", torch.float32)
+    n, E = logits.shape
+    idx = torch.empty((n, top), dtype=torch.int32, device=logits.device)
+    wt = torch.empty((n, top), dtype=torch.float32, device=logits.device)
+    check(l.gi_router_topk(_ptr(logits), logits.stride(0), E, int(top), _ptr(idx), _ptr(wt), n, _stream()), l)
+    return idx, wt
+
+
+def moe_rowwise(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, idx: torch.Tensor, wt: torch.Tensor,
+                activation: str) -> torch.Tensor:
+    """sum_j wt[t, j] W_down[idx[t, j]] act(W_up[idx[t, j]] x[t]) with the chosen experts read from device memory:
+    w_up [E, ff, hidden], w_down [E, hidden, ff]; one row of x at a time (decode steps)."""
+    l = require_gpu()
+    _rows(x, "x"), _dense(w_up, "w_up", x.dtype), _dense(w_down, "w_down", x.dtype)
+    _dense(idx, "idx", torch.int32), _dense(wt, "wt", torch.float32)
+    n, hidden = x.shape
+    E, ff, _ = w_up.shape
+    top = idx.shape[1]
+    a = torch.empty((n, top, ff), dtype=x.dtype, device=x.device)
+    y = torch.empty((n, hidden), dtype=x.dtype, device=x.device)
+    act = {"relu_squared": 0, "silu": 1}[activation]
+    check(l.gi_moe_up(_ptr(x), x.stride(0), _ptr(w_up), _ptr(idx), _ptr(a), code(x.dtype), n, top, E, ff, hidden, act,
+                      _stream()), l)
+    check(l.gi_moe_down(_ptr(a), _ptr(w_down), _ptr(idx), _ptr(wt), _ptr(y), code(x.dtype), n, top, E, ff, hidden,
+                        _stream()), l)
+    return y
+
+
+def moe_combine(buf: torch.Tensor, where: torch.Tensor, wt: torch.Tensor) -> torch.Tensor:
+    """y[t] = sum_j wt[t, j] buf[where[t, j]] (float32 sums in the order of j)."""
+    l = require_gpu()
+    _dense(buf, "buf"), _dense(where, "where", torch.int32), _dense(wt, "wt", torch.float32)
+    n, top = wt.shape
+    y = torch.empty((n, buf.shape[1]), dtype=buf.dtype, device=buf.device)
+    check(l.gi_moe_combine(_ptr(buf), _ptr(where), _ptr(wt), _ptr(y), code(buf.dtype), n, top, buf.shape[1], _stream()), l)
+    return y
+
+
 def _rows(t: torch.Tensor, name: str, dtype=None) -> torch.Tensor:
     """A 2-D tensor whose rows are dense but may lie apart (columns of a wider product's output)."""
     if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1:
@@ -272,16 +466,18 @@ def scan_state_floats(key_dim: int, value_dim: int) -> int:
     return int(n)
 
 
-def causal_conv_silu(x: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, tok_slot: torch.Tensor) -> torch.Tensor:
-    """silu of the causal convolution over time of x [n, C] (rows may lie apart) with taps [C, K], the K-1 inputs
+def causal_conv_silu(x: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, tok_slot: torch.Tensor,
+                     activation: str = "silu") -> torch.Tensor:
+    """silu (or, with activation "none", the plain sum) of the causal convolution over time of x [n, C] (rows may lie apart) with taps [C, K], the K-1 inputs
     before the step's first token of a sequence taken from `state` [slots, >= (K-1) C] (a view of float32 state
     rows); returns float32 [n, C].  Call `conv_state_update` afterwards."""
     l = require_gpu()
     _rows(x, "x"), _dense(taps, "taps"), _rows(state, "state", torch.float32), _dense(tok_slot, "tok_slot", torch.int32)
     n, C = x.shape
     out = torch.empty((n, C), dtype=torch.float32, device=x.device)
-    check(l.gi_causal_conv_silu(_ptr(x), x.stride(0), code(x.dtype), C, _ptr(taps), code(taps.dtype), taps.shape[1],
-                                _ptr(state), state.stride(0), _ptr(tok_slot), _ptr(out), n, 0, _stream()), l)
+    check(l.gi_causal_conv(_ptr(x), x.stride(0), code(x.dtype), C, _ptr(taps), code(taps.dtype), taps.shape[1],
+                           _ptr(state), state.stride(0), _ptr(tok_slot), _ptr(out), n, 0,
+                           {"none": 0, "silu": 1}[activation], _stream()), l)
     return out
 
 
@@ -325,20 +521,26 @@ def decay_scan(qkv: torch.Tensor, offsets: tuple, decay: torch.Tensor, state: to
 
 def delta_scan(qkv: torch.Tensor, offsets: tuple, ab: torch.Tensor, ab_offsets: tuple, A_log: torch.Tensor,
                dt_bias: torch.Tensor, state: torch.Tensor, spans: Optional[torch.Tensor], tok_slot: torch.Tensor,
-               n_heads: int, n_kv_heads: int, key_dim: int, value_dim: int, unit_eps: float) -> torch.Tensor:
+               n_heads: int, n_kv_heads: int, key_dim: int, value_dim: int, unit_eps: float,
+               channel_decay: bool = False, decay_logits: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The gated delta rule over the step's rows, from and to `state`.  `qkv` float32 [n, C] holds q, k (per key
     head) and v (per head) at `offsets`; `ab` float32 holds the logits of beta and of the decay at `ab_offsets`
-    (one column per head).  Returns float32 [n, n_heads * value_dim]."""
+    (one column per head; with `channel_decay` the decay has one column per head and key channel, and dt_bias as
+    many elements).  `decay_logits`: the decay's logits as a float32 matrix of their own (its column
+    ab_offsets[1] is the first).  Returns float32 [n, n_heads * value_dim]."""
     l = require_gpu()
     _rows(qkv, "qkv", torch.float32), _rows(ab, "ab", torch.float32), _rows(state, "state", torch.float32)
     _dense(A_log, "A_log"), _dense(dt_bias, "dt_bias", A_log.dtype)
     n = qkv.shape[0]
     spans, n_seq = _scan_args(spans, tok_slot, n)
     out = torch.empty((n, n_heads * value_dim), dtype=torch.float32, device=qkv.device)
+    if decay_logits is not None:
+        _rows(decay_logits, "decay_logits", torch.float32)
     check(l.gi_delta_scan(_ptr(qkv), qkv.stride(0), *map(int, offsets), _ptr(ab), ab.stride(0),
-                          *map(int, ab_offsets), _ptr(A_log), _ptr(dt_bias), code(A_log.dtype), _ptr(state),
+                          *map(int, ab_offsets), _ptr(decay_logits),
+                          decay_logits.stride(0) if decay_logits is not None else 0, _ptr(A_log), _ptr(dt_bias), code(A_log.dtype), _ptr(state),
                           state.stride(0), _ptr(spans), _ptr(tok_slot), _ptr(out), n_seq, n_heads, n_kv_heads,
-                          key_dim, value_dim, float(unit_eps), float(key_dim) ** -0.5, _stream()), l)
+                          key_dim, value_dim, float(unit_eps), float(key_dim) ** -0.5, int(channel_decay), _stream()), l)
     return out
 
 

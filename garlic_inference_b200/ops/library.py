@@ -24,7 +24,7 @@ P, I, L, F = c_void_p, c_int, c_longlong, c_float
 
 _SIGNATURES = {
     "gi_device_arch": ([], I),
-    "gi_embedding": ([P, P, I, P, I, I, I, P], I),
+    "gi_embedding": ([P, P, I, P, I, I, I, F, P], I),
     "gi_add_rmsnorm": ([P, P, P, I, P, I, P, I, I, F, I, P], I),
     "gi_residual_add": ([P, I, P, L, P], I),
     "gi_swiglu": ([P, P, I, I, I, P], I),
@@ -32,13 +32,26 @@ _SIGNATURES = {
     "gi_qk_norm_rope_append": ([P, P, P, P, I, P, P, I, F, P, P, I, P, P, P,
                                 I, I, I, I, I, I, I, I, I, P, P], I),
     "gi_attention_generic": ([P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P, I, I, P, P], I),
+    "gi_attention_masked": ([P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P, I, I, P, I, I, I, I, P, P], I),
+    "gi_attn_prepare": ([P, I, L, I, I, I, P, I, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P], I),
+    "gi_attn_finish": ([P, I, I, P, F, I, F, P, L, P, L, I, I, I, I, P], I),
+    "gi_add_dyt": ([P, P, I, P, P, P, P, I, P, I, P, I, I, I, P], I),
+    "gi_residual_add_scaled": ([P, I, P, I, P, I, I, P], I),
+    "gi_glu": ([P, L, P, I, I, I, I, P], I),
+    "gi_relu_squared": ([P, P, I, L, P], I),
+    "gi_scaled_sum": ([P, F, P, F, P, I, L, P], I),
+    "gi_router_topk": ([P, L, I, I, P, P, I, P], I),
+    "gi_moe_up": ([P, L, P, P, P, I, I, I, I, I, I, I, P], I),
+    "gi_moe_down": ([P, P, P, P, P, I, I, I, I, I, I, P], I),
+    "gi_moe_combine": ([P, P, P, P, I, I, I, I, P], I),
+    "gi_causal_conv": ([P, L, I, I, P, I, I, P, L, P, P, I, I, I, P], I),
     "gi_gate_norm_add": ([P, L, P, L, P, I, P, I, P, P, I, I, I, F, P], I),
     "gi_xielu": ([P, L, P, I, P, I, I, I, P], I),
     "gi_gated_group_rmsnorm": ([P, P, L, P, I, I, P, I, I, I, I, F, I, P], I),
     "gi_causal_conv_silu": ([P, L, I, I, P, I, I, P, L, P, P, I, I, P], I),
     "gi_scan_state_floats": ([I, I], L),
     "gi_decay_scan": ([P, L, I, I, I, I, P, P, L, P, P, P, I, I, I, I, P], I),
-    "gi_delta_scan": ([P, L, I, I, I, P, L, I, I, P, P, I, P, L, P, P, P, I, I, I, I, I, F, F, P], I),
+    "gi_delta_scan": ([P, L, I, I, I, P, L, I, I, P, L, P, P, I, P, L, P, P, P, I, I, I, I, I, F, F, I, P], I),
     "gi_causal_sink_softmax": ([P, L, P, L, I, I, I, I, I, F, P, I, P], I),
     "gi_latent_decode": ([P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, I, P, P], I),
     "gi_latent_prepare": ([P, L, I, I, P, I, P, I, F, P, F, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, P], I),

@@ -2,15 +2,21 @@
 from .base import (Block, Embedding, FeedForward, Gate, Head, Mixer, Norm, Part, PositionEncoding, Runtime,
                    StepContext, StepShape, known_parts, part_class, register_part)
 from .attention import GQAAttention
-from .block import LinearHead, PostNormGatedResidualBlock, PreNormResidualBlock, SigmoidGate, TokenEmbedding
+from .block import (ChannelScale, LinearHead, PostNormGatedResidualBlock, PreNormResidualBlock,
+                    PreNormScaledResidualBlock, SigmoidGate, TokenEmbedding)
 from .delta_rule import GatedDeltaRule
 from .latent_attention import LatentAttention
 from .linear_attention import DecayLinearAttention
-from .mlp import SwiGLUMLP, XieluMLP
-from .norm import RMSNorm
+from .masked_attention import MaskedAttention
+from .mlp import GluMLP, SwiGLUMLP, XieluMLP
+from .moe import RoutedExperts
+from .norm import DynamicTanhNorm, RMSNorm
+from .parallel import ParallelMixers
 from .rotary import RotaryPositions
 
 __all__ = ["Block", "Embedding", "FeedForward", "Gate", "Head", "PostNormGatedResidualBlock", "SigmoidGate",
            "GatedDeltaRule", "LatentAttention", "DecayLinearAttention", "XieluMLP", "Mixer", "Norm", "Part", "PositionEncoding",
            "Runtime", "StepContext", "StepShape", "known_parts", "part_class", "register_part", "GQAAttention",
-           "LinearHead", "PreNormResidualBlock", "TokenEmbedding", "SwiGLUMLP", "RMSNorm", "RotaryPositions"]
+           "LinearHead", "PreNormResidualBlock", "TokenEmbedding", "SwiGLUMLP", "RMSNorm", "RotaryPositions",
+           "ChannelScale", "PreNormScaledResidualBlock", "MaskedAttention", "GluMLP", "RoutedExperts",
+           "DynamicTanhNorm", "ParallelMixers"]

@@ -106,6 +106,9 @@ class StepContext:
     # float32 stream (blocks whose sublayers read the stream itself hand it from one to the next; any block
     # that changes the stream without renewing this copy sets it back to None).
     residual_act: Optional[torch.Tensor] = None
+    # A factor per channel (float32 or the weights' type, [hidden]) that the pending delta is multiplied by when
+    # it is added to the stream, set by blocks whose sublayer results join through a learned scale; None: 1.
+    delta_scale: Optional[torch.Tensor] = None
 
     def seq_spans(self) -> Optional[torch.Tensor]:
         """int32 [n_seq, 3] = {slot, first row, rows} on the device for kernels that walk each sequence's rows
@@ -169,7 +172,9 @@ class FeedForward(Part):
 
 
 class Norm(Part):
-    def add_norm(self, delta, residual, rows=None, write_residual=True):
+    def add_norm(self, delta, residual, rows=None, write_residual=True, delta_scale=None):
+        """normed(residual + delta * delta_scale); `delta_scale` (a factor per channel) is only passed by
+        arrangements that scale their sublayers' results, so a norm for other arrangements may leave it out."""
         raise NotImplementedError
 
 

@@ -12,6 +12,12 @@ is made from the sublayer's input:
 Gate, norm and add are one float32 kernel, which also leaves the new stream
 in the activation type for the products that read it next; nothing is pending
 when the block returns.  The feed-forward and either gate may be absent.
+
+`pre_norm_scaled_residual` (no upstream counterpart): pre-norm with a learned factor per channel (layer
+scale) on each sublayer's result:
+    h += s1 * mixer(norm_in(h));  h += s2 * ffn(norm_post(h))
+The scaled add happens inside the norm that follows, in float32; the block returns its last result pending and
+leaves the factor it still has to be multiplied by in `ctx.delta_scale`.  The feed-forward may be absent.
 """
 from __future__ import annotations
 
@@ -20,6 +26,16 @@ import torch
 from ..ops import kernels, linear
 from ..weights.loader import TensorWant
 from .base import Block, Embedding, Gate, Head, register_part
+
+
+def settle_scaled(delta, residual, ctx):
+    """A pending delta that still carries a factor per channel (left by a block with layer scale) is added to the
+    stream now; returns what is still pending.  Blocks whose norms take no such factor call this first."""
+    if delta is not None and ctx.delta_scale is not None:
+        kernels.residual_add_scaled(delta, ctx.delta_scale, residual)
+        delta = None
+    ctx.delta_scale = None
+    return delta
 
 
 class PreNormResidualBlock(Block):
@@ -47,6 +63,7 @@ class PreNormResidualBlock(Block):
 
     def step(self, delta, residual, ctx, cache, writes_cache=True):
         ctx.residual_act = None                     # this block changes the stream and keeps no rounded copy
+        delta = settle_scaled(delta, residual, ctx)
         x = self.norm_in.add_norm(delta, residual)
         a = self.mixer.step(x, ctx, cache, self.position, writes_cache)
         x = self.norm_post.add_norm(a, residual)
@@ -107,6 +124,7 @@ class PostNormGatedResidualBlock(Block):
 
     def step(self, delta, residual, ctx, cache, writes_cache=True):
         act = self.rt.dtype
+        delta = settle_scaled(delta, residual, ctx)
         if delta is not None:                       # a block before this one left its result pending
             kernels.residual_add(delta, residual)
             ctx.residual_act = None
@@ -125,8 +143,64 @@ class PostNormGatedResidualBlock(Block):
         return None
 
 
+class ChannelScale(Gate):
+    """A learned factor per channel on a sublayer's result (layer scale).  It does not depend on the input: the
+    arrangement hands `weight` to the kernel that adds the result to the stream."""
+    kind = "channel_scale"
+    graph_safe = True
+
+    @classmethod
+    def wanted(cls, params):
+        return {"weight": TensorWant((params["hidden_size"],), "norm")}
+
+    def __init__(self, params, load, rt):
+        super().__init__(params, load, rt)
+        self.weight = load("weight")
+
+
+class PreNormScaledResidualBlock(Block):
+    kind = "pre_norm_scaled_residual"
+
+    def __init__(self, mixer, feed_forward, norms, position, rt, gates=None):
+        self.rt = rt
+        self.mixer, self.feed_forward, self.position = mixer, feed_forward, position
+        gates = gates or {}
+        need = ["input"] + (["post_mixer"] if feed_forward is not None else [])
+        missing = [n for n in need if n not in norms]
+        if missing:
+            raise ValueError(f"block 'pre_norm_scaled_residual' needs norms {need}; missing {missing}")
+        self.norm_in, self.norm_post = norms["input"], norms.get("post_mixer")
+        self.scale_mixer, self.scale_ff = gates.get("mixer"), gates.get("ff")
+
+    def cache_requirement(self):
+        return self.mixer.cache_requirement()
+
+    @property
+    def graph_safe(self):
+        parts = (self.mixer, self.feed_forward, self.norm_in, self.norm_post, self.scale_mixer, self.scale_ff,
+                 self.position)
+        return all(p.graph_safe for p in parts if p is not None)
+
+    def step_arrays(self, shape, cache):
+        ff = self.feed_forward.step_arrays(shape, cache) if self.feed_forward is not None else {}
+        return {**self.mixer.step_arrays(shape, cache), **ff}
+
+    def step(self, delta, residual, ctx, cache, writes_cache=True):
+        ctx.residual_act = None
+        scale = lambda g: g.weight if g is not None else None
+        x = self.norm_in.add_norm(delta, residual, delta_scale=ctx.delta_scale if delta is not None else None)
+        y = self.mixer.step(x, ctx, cache, self.position, writes_cache)
+        ctx.delta_scale = scale(self.scale_mixer)
+        if self.feed_forward is not None:
+            x = self.norm_post.add_norm(y, residual, delta_scale=ctx.delta_scale)
+            y = self.feed_forward.step(x, ctx)
+            ctx.delta_scale = scale(self.scale_ff)
+        return y
+
+
 class TokenEmbedding(Embedding):
-    """h[t] = table[id[t]], no scaling (src/src-cuda/embedding.cu:29-53), written as float32."""
+    """h[t] = table[id[t]] * scale (src/src-cuda/embedding.cu:29-53, which has no scale: the default 1), written
+    as float32."""
     kind = "token_embedding"
     graph_safe = True
 
@@ -137,9 +211,10 @@ class TokenEmbedding(Embedding):
     def __init__(self, params, load, rt):
         super().__init__(params, load, rt)
         self.weight = load("weight")
+        self.scale = float(params.get("scale", 1.0))
 
     def step(self, ctx):
-        return kernels.embedding(ctx.tokens, self.weight)
+        return kernels.embedding(ctx.tokens, self.weight, scale=self.scale)
 
 
 class LinearHead(Head):
@@ -161,6 +236,8 @@ class LinearHead(Head):
 
 register_part(PreNormResidualBlock.kind, PreNormResidualBlock)
 register_part(PostNormGatedResidualBlock.kind, PostNormGatedResidualBlock)
+register_part(PreNormScaledResidualBlock.kind, PreNormScaledResidualBlock)
 register_part(SigmoidGate.kind, SigmoidGate)
+register_part(ChannelScale.kind, ChannelScale)
 register_part(TokenEmbedding.kind, TokenEmbedding)
 register_part(LinearHead.kind, LinearHead)

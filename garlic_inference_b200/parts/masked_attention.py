@@ -1,0 +1,151 @@
+"""Softmax attention with the options that grouped-query attention proper does not have, as a mixer.
+
+    q = Wq x, k = Wk x, v = Wv x                    `n_heads` query heads, `n_kv_heads` key/value heads; keys of
+                                                    `key_dim`, values of `value_dim` (they may differ)
+    conv_taps K > 0:  q, k, v <- causal convolution over time per channel (K taps, no bias, no activation); the
+                      last K - 1 projected values of a sequence are part of its state
+    a position part:  its rotation on q and k (any layout, any number of rotated dimensions)
+    mask:             "causal"; "window" (the last `size` keys); "chunk" (the keys j <= i with floor(j / size) =
+                      floor(i / size), chunks counted from position 0)
+    maps = 2:         differential attention.  Wq and Wk make two maps per head, laid out head by head as
+                      [map 1, map 2]; each is a softmax of its own over the same values, and
+                      o = a_1 - lam a_2,  lam = exp(lq1 . lk1) - exp(lq2 . lk2) + diff     (one number per layer)
+    sub_norm_eps:     o <- o / sqrt(mean(o^2) + eps) per head (no weight), times `out_mul`
+    head_gate:        o <- o * sigmoid(Wg x)_head, one number per head, from the mixer's own input
+    y = Wo concat(o)
+
+Query head h reads key/value head h // (n_heads // n_kv_heads).  With `own_kv` False the layer has no key and
+value tensors: the schedule points it at another layer's cache entry, whose keys and values (as that cache holds
+them: after convolution and rotation) it reads with its own queries, mask and everything else.
+
+All projections that read x are one packed product.  Scores, softmax and the weighted sums are float32 (the
+exact-order kernel: a position's result does not depend on how the tokens were cut into steps); what comes out
+of it is combined, normed and gated in float32 and rounded once.  Upstream has grouped-query attention only
+(src/models/qwen3/qwen3.cpp:140-179).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache import EntryRequirement, KVRequirement, StateRequirement
+from ..ops import kernels, linear
+from ..weights.loader import TensorWant
+from .base import Mixer, register_part
+from .linear_attention import pack_rows
+
+
+class MaskedAttention(Mixer):
+    kind = "masked_attention"
+    graph_safe = True
+
+    @staticmethod
+    def _sizes(params):
+        H, G, d, dv = (int(params[k]) for k in ("n_heads", "n_kv_heads", "key_dim", "value_dim"))
+        maps = int(params.get("maps", 1))
+        return H, G, d, dv, maps, int(params.get("conv_taps", 0) or 0), bool(params.get("own_kv", True))
+
+    @classmethod
+    def wanted(cls, params):
+        hid = params["hidden_size"]
+        H, G, d, dv, maps, K, own = cls._sizes(params)
+        w = {"q": TensorWant((H * maps * d, hid)), "o": TensorWant((hid, H * dv))}
+        if own:
+            w["k"], w["v"] = TensorWant((G * maps * d, hid)), TensorWant((G * dv, hid))
+        if K:
+            taps = lambda rows: TensorWant((rows, K), std_scale=8.0)
+            w["q.conv"] = taps(H * maps * d)
+            if own:
+                w["k.conv"], w["v.conv"] = taps(G * maps * d), taps(G * dv)
+        if maps == 2:
+            for n in ("lq1", "lk1", "lq2", "lk2"):
+                w[n] = TensorWant((d,), std_scale=5.0)
+        if params.get("head_gate", False):
+            w["g"] = TensorWant((H, hid))
+        return w
+
+    def __init__(self, params, load, rt):
+        super().__init__(params, load, rt)
+        self.hidden = int(params["hidden_size"])
+        self.H, self.G, self.d, self.dv, self.maps, self.K, self.own_kv = self._sizes(params)
+        if self.H % self.G:
+            raise ValueError(f"{self.H} query heads are no multiple of {self.G} key/value heads")
+        if self.maps not in (1, 2):
+            raise ValueError(f"{self.maps} softmax maps per head: one, or two (differential attention)")
+        self.scale = float(params.get("softmax_scale", self.d ** -0.5))
+        mask = params.get("mask") or {"kind": "causal"}
+        if mask["kind"] not in ("causal", "window", "chunk"):
+            raise ValueError(f"mask kind {mask['kind']!r} is none of 'causal', 'window', 'chunk'")
+        self.window = int(mask["size"]) if mask["kind"] == "window" else 0
+        self.chunk = int(mask["size"]) if mask["kind"] == "chunk" else 0
+        self.sub_norm_eps = params.get("sub_norm_eps")
+        self.out_mul = float(params.get("out_mul", 1.0))
+        self.head_gate = bool(params.get("head_gate", False))
+        self.Cq = self.H * self.maps * self.d
+        self.Ck, self.Cv = (self.G * self.maps * self.d, self.G * self.dv) if self.own_kv else (0, 0)
+        self.C = self.Cq + self.Ck + self.Cv
+        packed = [("q", self.Cq)] + ([("k", self.Ck), ("v", self.Cv)] if self.own_kv else []) + \
+                 ([("g", self.H)] if self.head_gate else [])
+        self.w_in, offs = pack_rows(load, packed, self.hidden, rt)
+        self.g_off = offs[-1] if self.head_gate else None
+        self.w_o = load("o")
+        self.taps = None
+        if self.K:
+            names = ["q.conv"] + (["k.conv", "v.conv"] if self.own_kv else [])
+            self.taps = torch.cat([load(n) for n in names]).contiguous()
+        self.lam = None
+        if self.maps == 2:
+            f = lambda n: load(n).to(torch.float32)
+            self.lam = (torch.exp((f("lq1") * f("lk1")).sum()) - torch.exp((f("lq2") * f("lk2")).sum())
+                        + float(params.get("diff", 0.0))).reshape(1).contiguous()
+        self.state_floats = -(-((self.K - 1) * self.C) // 4) * 4 if self.K > 1 else 0
+        self._no_state = None
+
+    def cache_requirement(self):
+        kv = KVRequirement(self.G * self.maps, self.d, None, 2, value_heads=self.G, value_dim=self.dv)
+        if not self.state_floats:
+            return kv
+        return EntryRequirement(kv, StateRequirement((self.state_floats,), torch.float32))
+
+    def _rotation(self, position):
+        if position is None:
+            return None, 0, False
+        freq, magnitude, n_rot, layout = position.rotary_frequencies()
+        if magnitude != 1.0:
+            raise ValueError("masked_attention turns q and k by plain angles: a rotation that scales cos and sin is "
+                             "not computed here")
+        if n_rot > self.d:
+            raise ValueError(f"{n_rot} rotated dimensions of heads of {self.d}")
+        return freq, n_rot, layout == "half"
+
+    def step(self, x, ctx, cache, position, writes_cache=True):
+        return linear(self.pre_output(x, ctx, cache, position, writes_cache), self.w_o)
+
+    def pre_output(self, x, ctx, cache, position, writes_cache=True):
+        """Everything before the output projection: [n, n_heads * value_dim] in the activation type."""
+        kv = cache.kv
+        if self.own_kv != bool(writes_cache):
+            raise ValueError("a layer with keys and values of its own writes its cache entry, and one without reads "
+                             "another layer's: the schedule says otherwise")
+        proj = linear(x, self.w_in)
+        src = proj
+        if self.K:
+            conv_in = proj[:, :self.C]
+            if self.K > 1:
+                src = kernels.causal_conv_silu(conv_in, self.taps, cache.state, ctx.tok_slot, activation="none")
+                kernels.conv_state_update(conv_in, self.K, cache.state, ctx.tok_slot)
+            else:                                     # one tap: a factor per channel, no state
+                if self._no_state is None:
+                    self._no_state = torch.zeros((cache.kv.block_table.shape[0] + 1, 4), dtype=torch.float32, device=x.device)
+                src = kernels.causal_conv_silu(conv_in, self.taps, self._no_state, ctx.tok_slot, activation="none")
+        freq, n_rot, half = self._rotation(position)
+        q = kernels.attn_prepare(src, 0, self.Cq if self.own_kv else -1, self.Cq + self.Ck, freq, n_rot, half,
+                                 ctx.tok_pos, ctx.tok_slot, kv.block_table, kv.k_pool, kv.v_pool, self.H * self.maps,
+                                 self.d, self.rt.dtype, ctx.status, append=writes_cache)
+        att = kernels.attention_masked(q, kv.k_pool, kv.v_pool, kv.block_table, ctx.tok_pos, ctx.tok_slot, self.scale,
+                                       ctx.status, window=self.window, chunk=self.chunk, maps=self.maps,
+                                       out_float32=True)
+        gate = proj[:, self.g_off:self.g_off + self.H] if self.head_gate else None
+        return kernels.attn_finish(att, self.H, self.maps, self.lam, self.sub_norm_eps, self.out_mul, gate, self.rt.dtype)
+
+
+register_part(MaskedAttention.kind, MaskedAttention)

@@ -10,7 +10,11 @@ rounding.  Upstream has no such feed-forward.
 (src/models/qwen3/qwen3.cpp:186-203).  gate and up are packed into one weight
 at load time (one product instead of two); silu and the product are one kernel
 in float32 with a single rounding (upstream rounds after silu and again after
-the product, src/src-cuda/activations/silu.cu:35-67, hadamard.cu:48-67)."""
+the product, src/src-cuda/activations/silu.cu:35-67, hadamard.cu:48-67).
+
+`glu_mlp`: down( act(gate(x)) * up(x) ) with `activation` "silu" or "gelu_tanh" (the tanh form of gelu,
+0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))); gate and up packed like SwiGLU's.  With "silu" it runs
+SwiGLU's fused products."""
 from __future__ import annotations
 
 import torch
@@ -42,6 +46,32 @@ class SwiGLUMLP(FeedForward):
         return linear(swiglu_product(x, self.w_gate_up), self.w_down)
 
 
+class GluMLP(FeedForward):
+    kind = "glu_mlp"
+    graph_safe = True
+
+    @classmethod
+    def wanted(cls, params):
+        h, i = params["hidden_size"], params["intermediate_size"]
+        return {"gate": TensorWant((i, h)), "up": TensorWant((i, h)), "down": TensorWant((h, i))}
+
+    def __init__(self, params, load, rt):
+        super().__init__(params, load, rt)
+        self.hidden, self.inter = int(params["hidden_size"]), int(params["intermediate_size"])
+        self.activation = params.get("activation", "silu")
+        if self.activation not in ("silu", "gelu_tanh"):
+            raise ValueError(f"glu_mlp activation {self.activation!r} is neither 'silu' nor 'gelu_tanh'")
+        self.w_gate_up = torch.empty((2 * self.inter, self.hidden), dtype=load.dtype("gate", "up"), device=rt.device)
+        load("gate", out=self.w_gate_up[:self.inter])
+        load("up", out=self.w_gate_up[self.inter:])
+        self.w_down = load("down")
+
+    def step(self, x, ctx):
+        if self.activation == "silu":
+            return linear(swiglu_product(x, self.w_gate_up), self.w_down)
+        return linear(kernels.glu(linear(x, self.w_gate_up), self.activation), self.w_down)
+
+
 class XieluMLP(FeedForward):
     kind = "xielu_mlp"
     graph_safe = True
@@ -60,4 +90,5 @@ class XieluMLP(FeedForward):
 
 
 register_part(SwiGLUMLP.kind, SwiGLUMLP)
+register_part(GluMLP.kind, GluMLP)
 register_part(XieluMLP.kind, XieluMLP)

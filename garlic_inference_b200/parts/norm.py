@@ -1,6 +1,15 @@
-"""RMSNorm: y = x * rsqrt(mean(x^2) + eps) * weight, the weight used as it is
-(src/src-cuda/norm.cu:3-49), fused with the residual add that precedes it
-(norm.cu:51-101).  `size` and `eps` are parameters; sums are float32."""
+"""Norms, each fused with the residual add that precedes it.
+
+`rms_norm`: y = x * rsqrt(mean(x^2) + eps) * weight, the weight used as it is
+(src/src-cuda/norm.cu:3-49; the add: norm.cu:51-101).  `size` and `eps` are
+parameters; sums are float32.
+
+`dyt_norm`, Dynamic Tanh: y = tanh(alpha x) * weight + bias with one learned
+number alpha; it takes no mean and no variance, so a row's elements do not
+depend on each other.  Upstream has no such norm.
+
+Both take `delta_scale`, a factor per channel on the pending delta (blocks
+with a learned layer scale)."""
 from __future__ import annotations
 
 from ..ops import kernels
@@ -22,11 +31,37 @@ class RMSNorm(Norm):
         self.eps = float(params["eps"])
         self.weight = load("weight")
 
-    def add_norm(self, delta, residual, rows=None, write_residual=True):
+    def add_norm(self, delta, residual, rows=None, write_residual=True, delta_scale=None):
         """normed(residual + delta) in the activation type.  The float32 sum is written back to
-        `residual` unless `rows` picks rows or `write_residual` is False; `delta` may be None."""
+        `residual` unless `rows` picks rows or `write_residual` is False; `delta` may be None.  A scaled delta
+        is added to the stream by a kernel of its own first (then the stream is written whatever was asked)."""
+        if delta is not None and delta_scale is not None:
+            kernels.residual_add_scaled(delta, delta_scale, residual)
+            delta = None
         return kernels.add_rmsnorm(delta, residual, self.weight, self.eps, self.rt.dtype, rows=rows,
                                    write_residual=write_residual)
 
 
+class DynamicTanhNorm(Norm):
+    kind = "dyt_norm"
+    graph_safe = True
+
+    @classmethod
+    def wanted(cls, params):
+        n = params["size"]
+        return {"weight": TensorWant((n,), "norm"), "bias": TensorWant((n,)), "alpha": TensorWant((), "norm")}
+
+    def __init__(self, params, load, rt):
+        super().__init__(params, load, rt)
+        self.size = int(params["size"])
+        dtype = load.dtype("weight", "bias", "alpha")
+        self.weight, self.bias = load("weight").to(dtype), load("bias").to(dtype)
+        self.alpha = load("alpha").to(dtype).reshape(1)
+
+    def add_norm(self, delta, residual, rows=None, write_residual=True, delta_scale=None):
+        return kernels.add_dyt(delta, delta_scale, residual, self.weight, self.bias, self.alpha, self.rt.dtype,
+                               rows=rows, write_residual=write_residual)
+
+
 register_part(RMSNorm.kind, RMSNorm)
+register_part(DynamicTanhNorm.kind, DynamicTanhNorm)

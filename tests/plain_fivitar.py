@@ -50,7 +50,7 @@ def read_safetensors(path) -> dict[str, torch.Tensor]:
         lo, hi = info["data_offsets"]
         arr = np.frombuffer(raw[8 + hlen + lo:8 + hlen + hi], dtype=_ST_DTYPES[info["dtype"]]).reshape(info["shape"])
         if info["dtype"] == "BF16":
-            out[name] = torch.from_numpy((arr.astype(np.uint32) << 16).view(np.float32).copy())
+            out[name] = torch.from_numpy((arr.astype(np.uint32).reshape(-1) << 16).view(np.float32).copy()).reshape(info["shape"])
         elif info["dtype"] in ("F32", "F16"):
             out[name] = torch.from_numpy(arr.astype(np.float32))
         else:
