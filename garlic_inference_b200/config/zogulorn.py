@@ -154,8 +154,6 @@ class ZogulornConfig:
             heads(m, at)
             if m["mask"]["size"] <= 0:
                 bad.append(f"{at}.mask.size must be positive, found {m['mask']['size']}")
-            if m["dim"] % 8:
-                bad.append(f"{at}.dim = {m['dim']}: this library's attention takes key sizes that are multiples of 8")
 
         for i, layer in enumerate(self.layers):
             m, at = layer["mixer"], f"layers[{i}].mixer"

@@ -1,5 +1,5 @@
 // Attention over the paged cache for any number of new tokens per sequence,
-// float32 or bfloat16, any head_dim that is a multiple of 8 up to 1024.
+// float32 or bfloat16, any head_dim up to 1024.
 //
 // This is the engine's exact path: the float32 engine uses it for prompts and
 // for decoding alike, and the bfloat16 engine uses it for head sizes its
@@ -111,9 +111,13 @@ attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const
             } else {
                 row = (((long long)page * n_kv + kvh) * page_size + (j % page_size)) * d;
                 vrow = (((long long)page * n_vh + vh) * page_size + (j % page_size)) * v_row;
-                const vec_t* kr = reinterpret_cast<const vec_t*>(k_pool + row);
                 float a = 0.f;
-                for (int i = 0; i < d / VN; ++i) a += dot_vec(kr[i], q_s + i * VN);
+                if (d % VN == 0) {               // rows start on 16 bytes: vector loads
+                    const vec_t* kr = reinterpret_cast<const vec_t*>(k_pool + row);
+                    for (int i = 0; i < d / VN; ++i) a += dot_vec(kr[i], q_s + i * VN);
+                } else {
+                    for (int i = 0; i < d; ++i) a = fmaf(to_f32(k_pool[row + i]), q_s[i], a);
+                }
                 s = a;
             }
         }
@@ -187,8 +191,8 @@ static int launch_generic(const void* q, const void* k_pool, const void* v_pool,
 }
 
 // The general entry point: everything the file's head lists.  `out` is written in the activation type unless
-// `out_f32` is given.  The key rows must be dense vectors of d elements (d a multiple of 8 for bfloat16, 4 for
-// float32: the vector loads); value rows may have any width.
+// `out_f32` is given.  Key rows whose width is a multiple of 16 bytes are read with vector loads, others
+// element by element; value rows may have any width.
 extern "C" int gi_attention_masked(const void* q, const void* k_pool, const void* v_pool, int act_dtype,
                                    const int* block_table, const int* tok_pos, const int* tok_slot,
                                    void* out, int n_tokens, int n_q, int n_kv, int d, int page_size,
@@ -198,7 +202,8 @@ extern "C" int gi_attention_masked(const void* q, const void* k_pool, const void
     GI_REQUIRE(n_tokens >= 0 && n_q > 0 && n_kv > 0 && d > 0, "gi_attention_generic: sizes must be positive");
     GI_REQUIRE(maps >= 1 && n_vh >= 1 && n_q % maps == 0 && n_kv == n_vh * maps && (n_q / maps) % n_vh == 0,
                "gi_attention_generic: %d query rows and %d key heads in %d maps over %d value heads", n_q, n_kv, maps, n_vh);
-    GI_REQUIRE(d % 8 == 0 && d <= 1024, "gi_attention_generic: head_dim %d must be a multiple of 8, at most 1024", d);
+    GI_REQUIRE(d <= 1024, "gi_attention_generic: head_dim %d is beyond 1024", d);
+    GI_REQUIRE((uintptr_t)k_pool % 16 == 0, "gi_attention_generic: the key pool must start on 16 bytes");
     GI_REQUIRE(n_q <= 65535, "gi_attention_generic: %d query heads is beyond 65535", n_q);
     GI_REQUIRE(d_v > 0 && d_v <= v_row && d_v <= 1024, "gi_attention_generic: %d value columns of rows of %d", d_v, v_row);
     GI_REQUIRE(page_size > 0 && max_pages > 0 && window >= 0 && chunk >= 0, "gi_attention_generic: page size, table width, window and chunk");
