@@ -555,6 +555,233 @@ def study_fivitar(args, pk) -> int:
     return 0
 
 
+# ---- the Zogulorn design beside Qwen3 at equal layer sizes -----------------------------------------
+def zogulorn_config_dict(width, heads, ff, vocab, n_layers, head_dim=128, chunk=1024, experts=16, top=2):
+    """`n_layers` layers that cycle through parallel + dense, attention + experts, parallel + experts and an
+    attention on the first attention's keys and values + dense, at sizes of a real model's layers."""
+    kv = max(1, heads // 4)
+    left = {"heads": heads, "kv_heads": kv, "dim": head_dim, "vdim": head_dim, "mask": {"size": chunk},
+            "rot": {"base": 250000.0, "dims": head_dim}, "scale": head_dim ** -0.5}
+    right = {"heads": heads // 2, "kv_heads": max(1, heads // 4), "dim": head_dim, "vdim": head_dim, "conv": 4,
+             "rank": max(8, width // 16)}
+    par = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 0.6, "right_scale": 1.1}}
+    att = lambda src: {"type": "attention",
+                       "mixer": dict({"heads": heads // 2, "kv_heads": max(1, kv // 2), "dim": head_dim // 2,
+                                      "vdim": head_dim, "mask": {"size": 2 * chunk}, "conv": 4, "diff": 0.6,
+                                      "scale": (head_dim // 2) ** -0.5}, **({"kv_from": src} if src is not None else {}))}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": max(64, ff * 3 // (2 * top) // 64 * 64)}, "router": {"experts": experts, "top": top}}
+    layers, first_att = [], None
+    for i in range(n_layers):
+        k = i % 4
+        if k in (0, 2):
+            layers.append(dict(par, mlp=dense if k == 0 else moe))
+        elif k == 1 or first_att is None:
+            first_att = i if first_att is None else first_att
+            layers.append(dict(att(None), mlp=moe))
+        else:
+            layers.append(dict(att(first_att), mlp=dense))
+    return {"architecture": "Zogulorn", "vocab": vocab, "width": width, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-6}, "layers": layers}
+
+
+def study_zogulorn(args, pk) -> int:
+    """Prefill (one prompt of 2,048 tokens) and decode (batches of 1, 8 and 64 with 2,048 cached tokens each) of
+    Zogulorn models with random weights, beside Qwen3 models of the same width, depth and heads with a
+    feed-forward of equal active parameters, and the design's kernels timed alone beside the closest kernels of
+    the other models.  One JSON line."""
+    import torch
+    from garlic_inference_b200 import LanguageModel, Qwen3Config
+    from garlic_inference_b200.config import ZogulornConfig
+    from garlic_inference_b200.ops import counters, kernels
+    from garlic_inference_b200.sampling import SamplingParams
+    K, W = min(args.steps, 64), max(min(args.warmup, 8), 3)
+    torch.cuda.set_device(0)
+    greedy = SamplingParams()
+    gen = torch.Generator().manual_seed(0)
+    sizes = [("1b", 2048, 16, 8192, 32000, 8), ("8b", 4096, 32, 18432, 32000, 4)]
+    out = {"study": "zogulorn", "dtype": "bfloat16", "data": "synthetic", "steps": K, "warmup": W,
+           "peaks": pk, "models": {}, "kernels": {}}
+
+    def timed(fn, reps=5, warm=3):
+        for _ in range(warm):
+            fn()
+        flush = torch.empty(160 << 20, dtype=torch.uint8, device="cuda")
+        ms = []
+        for _ in range(reps):
+            flush.zero_()                                  # larger than L2: the next run starts cold
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record()
+            torch.cuda.synchronize()
+            ms.append(a.elapsed_time(b))
+        return statistics.median(ms)
+
+    def run_model(cfg, vocab, active_bytes=None):
+        per_seq = -(-(CACHED + W + K + 8) // 64) * 64
+        model = LanguageModel.from_random(cfg, seed=0, device=0, dtype="bfloat16", max_tokens=64 * per_seq,
+                                          max_slots=64)
+        eng, sampler = model.engine, model.sampler
+        prompt = lambda n: torch.randint(0, vocab, (n,), generator=gen).tolist()
+        res = {"weight_bytes": model.model.weight_bytes()}
+
+        def prefill_once():
+            s = eng.alloc_slot()
+            model.step([(s, prompt(PREFILL_TOKENS), [PREFILL_TOKENS - 1])])
+            eng.free_slot(s)
+        ms = timed(prefill_once, reps=5, warm=3)
+        res["prefill"] = {"tokens": PREFILL_TOKENS, "ms": round(ms, 3), "tokens_per_s": round(PREFILL_TOKENS / ms * 1e3)}
+        for batch in (1, 8, 64):
+            slots, firsts = [], []
+            for _ in range(batch):
+                s = eng.alloc_slot()
+                firsts.append(sampler.sample(model.step([(s, prompt(CACHED), [CACHED - 1])]), greedy, [0], [0]))
+                slots.append(s)
+            toks = torch.cat(firsts)
+            for _ in range(W):
+                toks = sampler.sample(eng.step_decode_device(slots, toks), greedy, slots, slots)
+            torch.cuda.synchronize()
+            n0 = counters.launches
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(K):
+                toks = sampler.sample(eng.step_decode_device(slots, toks), greedy, slots, slots)
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / K
+            res[f"decode_b{batch}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(batch / ms * 1e3),
+                                       "launches_per_step": (counters.launches - n0) // K}
+            for s in slots:
+                eng.free_slot(s)
+        eng.check()
+        del model
+        torch.cuda.empty_cache()
+        return res
+
+    for label, width, heads, ff, vocab, n_layers in sizes:
+        zcfg = ZogulornConfig.from_dict(zogulorn_config_dict(width, heads, ff, vocab, n_layers))
+        qcfg = Qwen3Config(hidden_size=width, num_hidden_layers=n_layers, num_attention_heads=heads,
+                           num_key_value_heads=max(1, heads // 4), head_dim=128, intermediate_size=ff,
+                           vocab_size=vocab, max_position_embeddings=CONTEXT * 2)
+        out["models"][label] = {"width": width, "heads": heads, "ff": ff, "layers": n_layers,
+                                "zogulorn": run_model(zcfg, vocab), "qwen3": run_model(qcfg, vocab)}
+
+    # ---- the kernels alone, at the larger size: one prompt of 2,048 tokens, and 8 single tokens ----
+    width, H, G, d, T, page, chunk = 4096, 32, 8, 128, PREFILL_TOKENS, 64, 1024
+    dev = "cuda"
+    bf = lambda *shape: torch.randn(*shape, device=dev, dtype=torch.bfloat16) * 0.5
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    from garlic_inference_b200.parts import StepShape
+    from garlic_inference_b200.parts.attention import query_runs
+    from garlic_inference_b200.parts.linear_attention import scan_state_floats
+    kern = out["kernels"]
+
+    def note(name, ms, flops=0.0, bytes_=0.0):
+        kern[name] = {"ms": round(ms, 4)}
+        if flops:
+            kern[name]["tflops"] = round(flops / ms / 1e9, 2)
+            kern[name]["of_measured_bf16"] = round(flops / ms / 1e9 / pk["bf16_tflops"], 4)
+        if bytes_:
+            kern[name]["gbs"] = round(bytes_ / ms / 1e6, 1)
+            kern[name]["of_measured_copy"] = round(bytes_ / ms / 1e6 / pk["hbm_gbs"], 3)
+
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    table = torch.arange(8 * T // page, dtype=torch.int32, device=dev).view(8, T // page)
+    pos, slot0 = torch.arange(T, dtype=torch.int32, device=dev), i32([0] * T)
+    pos8, slots8 = i32([T - 1] * 8), i32(list(range(8)))
+    runs64 = torch.from_numpy(query_runs(StepShape([0], [0], [T], [0], False), 64)).to(dev)
+    runs128 = torch.from_numpy(query_runs(StepShape([0], [0], [T], [0], False), 128)).to(dev)
+    kp, vp = bf(8 * T // page, G, page, d), bf(8 * T // page, G, page, d)
+    q = bf(T, H, d)
+    seen = sum(min(p % chunk, p) + 1 for p in range(T))            # (query, key) pairs inside the chunks
+    # chunked attention for a prompt: the design's kernel, and the closest kernels (causal over all keys)
+    ms = timed(lambda: kernels.attention_prefill_masked_bf16(q, kp, vp, table, runs64, 0.088, chunk=chunk, rows_covered=True))
+    note("chunk_attention_prefill2048_mma", ms, flops=4.0 * H * d * seen)
+    ms = timed(lambda: kernels.attention_prefill_bf16(q, kp, vp, table, runs64, 0.088, 0, rows_covered=True))
+    note("gqa_attention_prefill2048_mma", ms, flops=4.0 * H * d * T * (T + 1) / 2)
+    ms = timed(lambda: kernels.attention_prefill_tcgen05(q, kp, vp, table, runs128, 0.088, 0, rows_covered=True))
+    note("gqa_attention_prefill2048_tcgen05", ms, flops=4.0 * H * d * T * (T + 1) / 2)
+    # differential attention for a prompt: two maps of 64 over values of 128 (exact-order kernel), 16 heads
+    Hd, Gd, dd = 16, 4, 64
+    kpd, qd2 = bf(8 * T // page, Gd * 2, page, dd), bf(T, Hd * 2, dd)
+    vpd = bf(8 * T // page, Gd, page, d)
+    seen2 = sum(min(p % (2 * chunk), p) + 1 for p in range(T))
+    ms = timed(lambda: kernels.attention_masked(qd2, kpd, vpd, table, pos, slot0, 0.125, status, chunk=2 * chunk, maps=2,
+                                                out_float32=True), reps=3, warm=1)
+    note("differential_attention_prefill2048_exact_order", ms, flops=2.0 * Hd * 2 * (dd + d) * seen2)
+    # decode steps: 8 sequences of 2,048 cached tokens
+    q8 = bf(8, H, d)
+    ms = timed(lambda: kernels.attention_masked(q8, kp, vp, table, pos8, slots8, 0.088, status, chunk=chunk, out_float32=True))
+    note("chunk_attention_decode_b8_exact_order", ms, bytes_=8 * (T - chunk) * 2 * G * d * 2)
+    ms = timed(lambda: kernels.attention_decode_tcgen05(q8, kp, vp, table, pos8, slots8, 0.088, 0))
+    note("gqa_attention_decode_b8_tcgen05", ms, bytes_=8 * T * 2 * G * d * 2)
+    q8d = bf(8, Hd * 2, dd)
+    ms = timed(lambda: kernels.attention_masked(q8d, kpd, vpd, table, pos8, slots8, 0.125, status, chunk=2 * chunk, maps=2,
+                                                out_float32=True))
+    note("differential_attention_decode_b8_exact_order", ms, bytes_=8 * T * (2 * Gd * dd + Gd * d) * 2)
+    # the delta rule's scan with a decay per key channel, beside the one with a decay per head
+    Hr, Hk = 16, 8
+    sf = Hr * scan_state_floats(d, d)
+    C = 2 * Hk * d + Hr * d
+    for n_rows, tag, spans, slots in ((T, "prefill2048", i32([[0, 0, T]]), i32([0] * T)),
+                                      (8, "decode_b8", None, i32(list(range(8))))):
+        state = torch.zeros(9, sf, device=dev)
+        conv_out = torch.randn(n_rows, C, device=dev)
+        b_log, a_head, a_chan = (torch.randn(n_rows, c, device=dev) for c in (Hr, Hr, Hr * d))
+        A, dt_h, dt_c = torch.zeros(Hr, device=dev), torch.zeros(Hr, device=dev), torch.zeros(Hr * d, device=dev)
+        seqs = 1 if spans is not None else 8
+        bytes_ = seqs * 2 * sf * 4 + n_rows * (C * 4 + Hr * d * 4)
+        ms = timed(lambda: kernels.delta_scan(conv_out, (0, Hk * d, 2 * Hk * d), b_log, (0, 0), A, dt_c, state, spans, slots,
+                                              Hr, Hk, d, d, 1e-6, channel_decay=True, decay_logits=a_chan))
+        note(f"delta_scan_channel_decay_{tag}", ms, flops=8.0 * n_rows * Hr * d * d, bytes_=bytes_ + n_rows * Hr * d * 4)
+        ms = timed(lambda: kernels.delta_scan(conv_out, (0, Hk * d, 2 * Hk * d), b_log, (0, 0), A, dt_h, state, spans, slots,
+                                              Hr, Hk, d, d, 1e-6, decay_logits=a_head))
+        note(f"delta_scan_head_decay_{tag}", ms, flops=8.0 * n_rows * Hr * d * d, bytes_=bytes_)
+    # the norm beside RMSNorm, the gated unit beside SwiGLU, at 2,048 rows
+    res, delta = torch.randn(T, width, device=dev), bf(T, width)
+    w, b, al, ls = bf(width), bf(width), bf(1), bf(width)
+    ms = timed(lambda: kernels.add_dyt(delta, ls, res, w, b, al, torch.bfloat16))
+    note("scaled_add_dyt_2048", ms, bytes_=T * width * (2 + 4 + 4 + 2))
+    ms = timed(lambda: kernels.add_rmsnorm(delta, res, w, 1e-6, torch.bfloat16))
+    note("add_rmsnorm_2048", ms, bytes_=T * width * (2 + 4 + 4 + 2))
+    gu = bf(T, 2 * 18432)
+    ms = timed(lambda: kernels.glu(gu, "gelu_tanh"))
+    note("gelu_glu_2048", ms, bytes_=T * 18432 * 6)
+    ms = timed(lambda: kernels.swiglu(gu))
+    note("swiglu_2048", ms, bytes_=T * 18432 * 6)
+    # routed experts: 16 experts of 13,824, 2 chosen; 8 rows (row by row) and 2,048 rows (expert by expert), beside a
+    # dense gated feed-forward of the same active size run through the same products
+    from garlic_inference_b200.ops import linear
+    from garlic_inference_b200.parts import Runtime, StepContext, part_class
+    E, top, eff = 16, 2, 13824
+
+    class Load:
+        def dtype(self, *a):
+            return torch.bfloat16
+
+        def __call__(self, n, out=None):
+            shape = (E, width) if n == "router" else ((eff, width) if n.endswith("up") else (width, eff))
+            t = bf(*shape) * 0.05
+            return t if out is None else out.copy_(t)
+
+    part = part_class("routed_experts")(dict(hidden_size=width, expert_size=eff, n_experts=E, top=top), Load(),
+                                        Runtime(torch.bfloat16, torch.device(dev)))
+    z = i32([0])
+    for n_rows in (8, T):
+        x = bf(n_rows, width)
+        ctx = StepContext(n_rows, z, z, z)
+        ms = timed(lambda: part.step(x, ctx))
+        active = min(E, n_rows * top) * 2 * eff * width * 2
+        note(f"routed_experts_{n_rows}_rows", ms, flops=4.0 * n_rows * top * eff * width, bytes_=active)
+    wgu, wd = bf(2 * 18432, width) * 0.05, bf(width, 18432) * 0.05
+    for n_rows in (8, T):
+        x = bf(n_rows, width)
+        ms = timed(lambda: linear(kernels.glu(linear(x, wgu), "gelu_tanh"), wd))
+        note(f"dense_gelu_glu_ff_{n_rows}_rows", ms, flops=6.0 * n_rows * 18432 * width, bytes_=3 * 18432 * width * 2)
+    kernels.check_bounded_waits(torch.device("cuda", 0))
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -568,7 +795,7 @@ def main() -> int:
     ap.add_argument("--write-model", default=None, metavar="DIR",
                     help="with --impl reference: only write the model folder that arm uses (tied head, --layers of the 36) "
                          "to DIR and exit, for running baseline/_ref/bin/reference_runner by hand or under a profiler")
-    ap.add_argument("--study", default=None, choices=["prefill-clocks", "fivitar"],
+    ap.add_argument("--study", default=None, choices=["prefill-clocks", "fivitar", "zogulorn"],
                     help="prefill-clocks: 40 prompt steps of 2,048 tokens back to back with the clock and the power "
                          "sampled every 20 ms; prints a table and no JSON line.  fivitar: prefill and decode of the "
                          "Fivitar design at two sizes of real layers beside Qwen3 at equal sizes, and the mixers' "
@@ -590,6 +817,8 @@ def main() -> int:
 
     if args.study == "fivitar":
         return study_fivitar(args, peaks())
+    if args.study == "zogulorn":
+        return study_zogulorn(args, peaks())
 
     import torch
     from garlic_inference_b200 import LanguageModel, Qwen3Config

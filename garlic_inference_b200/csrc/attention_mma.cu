@@ -25,7 +25,9 @@
 //            parameter; which keys a slice covers follows from the sequence's
 //            length on the device, so a recorded launch stays valid as the
 //            sequence grows.
-// Head sizes: multiples of 16 up to 128.
+// Head sizes: multiples of 16 up to 128; keys and values of one size, or one twice the other.
+// Both kernels also take a chunk mask, a key pool with heads of its own and strided queries and outputs (AttnLayout
+// below): what a mixer with several softmax maps per head over shared values needs.
 #include "common.cuh"
 #include <math.h>
 
@@ -62,6 +64,17 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Where the prompt kernel finds its operands when they are not the plain [rows, heads, D] and [pages, n_kv, page, D]:
+// a query row's elements start at row * q_ts + head * q_hs + q_o (the output's likewise), the key pool has n_kh
+// heads per page and query head h reads key head (h / group) * k_mul + k_add (the value pool keeps n_kv heads
+// and head h / group).  That is what a mixer with several softmax maps per head over the same values needs: map
+// m of a head lies at q_o = m D, reads key head kvh * maps + m, and writes beside the other maps.  chunk > 0: a
+// query sees only the keys of its own chunk of positions (chunks counted from position 0).
+struct AttnLayout {
+    long long q_ts, q_hs, q_o, o_ts, o_hs, o_o;
+    int n_kh, k_mul, k_add, chunk;
+};
+
 // Element offset of row j of a sequence inside a pool (for key/value head kvh), or -1 when j is not below
 // key_end or its page is not mapped.  No branch around the table read, so that a thread's reads for
 // several rows are issued together instead of one after the other.
@@ -76,25 +89,42 @@ __device__ __forceinline__ long long kv_row_offset(const int* __restrict__ bt_ro
 
 // Stage one tile of 64 keys (rows key0 .. key0+63 of the sequence) of keys and values into shared memory.
 // Rows at or beyond key_end, and rows whose page is not mapped, are zero-filled.
-template <int D>
+// Keys are rows of DK elements in a pool with n_kh heads per page (head kh), values rows of DV elements in a pool
+// with n_kv heads per page (head kvh).
+template <int DK, int DV>
 __device__ __forceinline__ void load_kv_tile(bf16* sK, bf16* sV, const bf16* __restrict__ k_pool,
                                              const bf16* __restrict__ v_pool, const int* __restrict__ bt_row,
                                              int key0, int key_end, int n_kv, int kvh, int page_size,
-                                             int max_pages, int n_pool_pages) {
-    constexpr int LD = D + 8, CH = D / 8, PASSES = AT_BN * CH / AT_THREADS;
-    long long off[PASSES];
+                                             int max_pages, int n_pool_pages, int n_kh, int kh) {
+    {
+        constexpr int LD = DK + 8, CH = DK / 8, PASSES = AT_BN * CH / AT_THREADS;
+        long long off[PASSES];
 #pragma unroll
-    for (int p = 0; p < PASSES; ++p)
-        off[p] = kv_row_offset(bt_row, key0 + (threadIdx.x + p * AT_THREADS) / CH, key_end, n_kv, kvh, page_size,
-                               max_pages, n_pool_pages, D);
+        for (int p = 0; p < PASSES; ++p)
+            off[p] = kv_row_offset(bt_row, key0 + (threadIdx.x + p * AT_THREADS) / CH, key_end, n_kh, kh, page_size,
+                                   max_pages, n_pool_pages, DK);
 #pragma unroll
-    for (int p = 0; p < PASSES; ++p) {
-        const int i = threadIdx.x + p * AT_THREADS;
-        const int r = i / CH, c = i % CH;
-        const bool valid = off[p] >= 0;
-        const size_t o = valid ? (size_t)off[p] + c * 8 : 0;
-        cp_async_16(sK + r * LD + c * 8, k_pool + o, valid);
-        cp_async_16(sV + r * LD + c * 8, v_pool + o, valid);
+        for (int p = 0; p < PASSES; ++p) {
+            const int i = threadIdx.x + p * AT_THREADS;
+            const int r = i / CH, c = i % CH;
+            const bool valid = off[p] >= 0;
+            cp_async_16(sK + r * LD + c * 8, k_pool + (valid ? (size_t)off[p] + c * 8 : 0), valid);
+        }
+    }
+    {
+        constexpr int LD = DV + 8, CH = DV / 8, PASSES = AT_BN * CH / AT_THREADS;
+        long long off[PASSES];
+#pragma unroll
+        for (int p = 0; p < PASSES; ++p)
+            off[p] = kv_row_offset(bt_row, key0 + (threadIdx.x + p * AT_THREADS) / CH, key_end, n_kv, kvh, page_size,
+                                   max_pages, n_pool_pages, DV);
+#pragma unroll
+        for (int p = 0; p < PASSES; ++p) {
+            const int i = threadIdx.x + p * AT_THREADS;
+            const int r = i / CH, c = i % CH;
+            const bool valid = off[p] >= 0;
+            cp_async_16(sV + r * LD + c * 8, v_pool + (valid ? (size_t)off[p] + c * 8 : 0), valid);
+        }
     }
 }
 
@@ -188,13 +218,14 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&m)[2],
 
 // ------------------------------------------------------------------------------ prefill
 // tiles[t] = {slot, first row of q, rows in the tile (<= 64), position of the first row}
-template <int D>
+template <int D, int DV>
 __global__ void __launch_bounds__(AT_THREADS)
 flash_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                      const int* __restrict__ block_table, const int4* __restrict__ tiles, bf16* __restrict__ out,
-                     int n_q, int n_kv, int page_size, int max_pages, int n_pool_pages, int window, float scale_log2) {
+                     int n_q, int n_kv, int page_size, int max_pages, int n_pool_pages, int window, float scale_log2,
+                     AttnLayout lay) {
     gi_pdl_start();
-    constexpr int LD = D + 8;
+    constexpr int LD = D + 8, LDV = DV + 8;
     extern __shared__ __align__(16) unsigned char at_smem[];
     bf16* sQ = reinterpret_cast<bf16*>(at_smem);
     bf16* sK = sQ + AT_BM * LD;
@@ -208,8 +239,11 @@ flash_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool
     const int* bt_row = block_table + (size_t)slot * max_pages;
 
     const int hi = pos0 + n_rows - 1;                                   // last position of the tile
-    const int lo = window > 0 ? max(0, pos0 - window + 1) : 0;          // first key any row of the tile sees
+    int lo = window > 0 ? max(0, pos0 - window + 1) : 0;                // first key any row of the tile sees
+    const int chunk = lay.chunk;
+    if (chunk > 0) lo = max(lo, pos0 / chunk * chunk);
     const int kt_lo = lo / AT_BN, n_tiles = hi / AT_BN - kt_lo + 1;
+    const int n_kh = lay.n_kh > 0 ? lay.n_kh : n_kv, kh = kvh * lay.k_mul + lay.k_add;
 
     {   // the queries of the tile, rows beyond n_rows zero-filled
         constexpr int CH = D / 8;
@@ -218,28 +252,32 @@ flash_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool
             const int i = threadIdx.x + p * AT_THREADS;
             const int r = i / CH, c = i % CH;
             const bool valid = r < n_rows;
-            const bf16* src = q + ((size_t)(row0 + (valid ? r : 0)) * n_q + h) * D + c * 8;
+            const bf16* src = q + (size_t)(row0 + (valid ? r : 0)) * lay.q_ts + (size_t)h * lay.q_hs + lay.q_o + c * 8;
             cp_async_16(sQ + r * LD + c * 8, src, valid);
         }
     }
-    load_kv_tile<D>(sK, sV, k_pool, v_pool, bt_row, kt_lo * AT_BN, hi + 1, n_kv, kvh, page_size, max_pages, n_pool_pages);
+    load_kv_tile<D, DV>(sK, sV, k_pool, v_pool, bt_row, kt_lo * AT_BN, hi + 1, n_kv, kvh, page_size, max_pages,
+                        n_pool_pages, n_kh, kh);
     cp_async_commit();
 
     uint32_t a[D / 16][4];
-    float o[D / 8][4];
+    float o[DV / 8][4];
 #pragma unroll
-    for (int dt = 0; dt < D / 8; ++dt)
+    for (int dt = 0; dt < DV / 8; ++dt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[dt][e] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     const int p_row[2] = {pos0 + warp * 16 + g, pos0 + warp * 16 + g + 8};      // positions of this thread's rows
     const int p_warp_max = pos0 + warp * 16 + 15;
+    // first key each of this thread's rows sees in its chunk, and the first any row of the warp sees
+    const int c_row[2] = {chunk > 0 ? p_row[0] / chunk * chunk : 0, chunk > 0 ? p_row[1] / chunk * chunk : 0};
+    const int c_warp = chunk > 0 ? (pos0 + warp * 16) / chunk * chunk : 0;
 
     for (int it = 0; it < n_tiles; ++it) {
         const int st = it & 1;
         if (it + 1 < n_tiles) {
-            load_kv_tile<D>(sK + (st ^ 1) * AT_BN * LD, sV + (st ^ 1) * AT_BN * LD, k_pool, v_pool, bt_row,
-                            (kt_lo + it + 1) * AT_BN, hi + 1, n_kv, kvh, page_size, max_pages, n_pool_pages);
+            load_kv_tile<D, DV>(sK + (st ^ 1) * AT_BN * LD, sV + (st ^ 1) * AT_BN * LDV, k_pool, v_pool, bt_row,
+                                (kt_lo + it + 1) * AT_BN, hi + 1, n_kv, kvh, page_size, max_pages, n_pool_pages, n_kh, kh);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -248,7 +286,8 @@ flash_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool
         __syncthreads();
         if (it == 0) load_a_frags<D>(a, sQ + warp * 16 * LD);
         const int key0 = (kt_lo + it) * AT_BN;
-        const bool warp_sees = key0 <= p_warp_max && (window <= 0 || key0 + AT_BN - 1 > pos0 + warp * 16 - window);
+        const bool warp_sees = key0 <= p_warp_max && (window <= 0 || key0 + AT_BN - 1 > pos0 + warp * 16 - window) &&
+                               key0 + AT_BN - 1 >= c_warp;
         if (warp_sees) {
             float s[AT_BN / 8][4];
             qk_product<D, AT_BN / 8>(s, a, sK + st * AT_BN * LD, 0);
@@ -258,13 +297,13 @@ flash_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool
                 for (int e = 0; e < 4; ++e) {
                     const int j = key0 + nt * 8 + 2 * t + (e & 1);
                     const int p = p_row[e >> 1];
-                    const bool ok = j <= p && (window <= 0 || j > p - window);
+                    const bool ok = j <= p && (window <= 0 || j > p - window) && j >= c_row[e >> 1];
                     s[nt][e] = ok ? s[nt][e] * scale_log2 : -INFINITY;
                 }
             }
             uint32_t pf[AT_BN / 16][4];
-            softmax_update<D, AT_BN / 8>(s, m, l, o, pf);
-            pv_product<D, AT_BN / 16>(o, pf, sV + st * AT_BN * LD, 0);
+            softmax_update<DV, AT_BN / 8>(s, m, l, o, pf);
+            pv_product<DV, AT_BN / 16>(o, pf, sV + st * AT_BN * LDV, 0);
         }
         __syncthreads();
     }
@@ -278,9 +317,9 @@ flash_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool
         const int r = warp * 16 + g + hh * 8;
         if (r >= n_rows) continue;
         const float inv = l[hh] > 0.f ? 1.f / l[hh] : 0.f;
-        bf16* dst = out + ((size_t)(row0 + r) * n_q + h) * D;
+        bf16* dst = out + (size_t)(row0 + r) * lay.o_ts + (size_t)h * lay.o_hs + lay.o_o;
 #pragma unroll
-        for (int dt = 0; dt < D / 8; ++dt)
+        for (int dt = 0; dt < DV / 8; ++dt)
             *reinterpret_cast<uint32_t*>(dst + dt * 8 + 2 * t) = pack_bf16(o[dt][hh * 2] * inv, o[dt][hh * 2 + 1] * inv);
     }
 }
@@ -288,16 +327,16 @@ flash_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool
 // ------------------------------------------------------------------------------ decode (split-KV)
 // part_o  [n_seqs, n_q, n_splits, D]  float32 unnormalised outputs
 // part_ml [n_seqs, n_q, n_splits, 2]  float32 (max in the log2 domain, sum)
-template <int D>
+template <int D, int DV>
 __global__ void __launch_bounds__(AT_THREADS)
 decode_splitkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                       const int* __restrict__ block_table, const int* __restrict__ tok_pos,
                       const int* __restrict__ tok_slot, float* __restrict__ part_o, float* __restrict__ part_ml,
                       int n_q, int n_kv, int page_size, int max_pages, int n_pool_pages, int window,
-                      float scale_log2, int n_splits) {
+                      float scale_log2, int n_splits, AttnLayout lay) {
     gi_pdl_launch_dependents();
-    constexpr int LD = D + 8, CH = D / 8;
-    constexpr int STAGE = 2 * 16 * LD;                           // elements of one warp's stage: 16 keys, 16 values
+    constexpr int LD = D + 8, CH = D / 8, LDV = DV + 8, CHV = DV / 8;
+    constexpr int STAGE = 16 * LD + 16 * LDV;                    // elements of one warp's stage: 16 keys, 16 values
     extern __shared__ __align__(16) unsigned char at_smem[];
     bf16* sQ = reinterpret_cast<bf16*>(at_smem);                // 16 rows
     bf16* sKV = sQ + 16 * LD;                                    // [4 warps][AT_DEC_DEPTH][keys | values][16][LD]
@@ -307,8 +346,10 @@ decode_splitkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_poo
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int slot = tok_slot[b], pos = tok_pos[b];
     const int kv_len = pos + 1;
-    const int lo = window > 0 ? max(0, kv_len - window) : 0;
+    int lo = window > 0 ? max(0, kv_len - window) : 0;
+    if (lay.chunk > 0) lo = max(lo, max(pos, 0) / lay.chunk * lay.chunk);
     const int lo_al = lo / AT_BN * AT_BN;
+    const int n_kh = lay.n_kh > 0 ? lay.n_kh : n_kv, kh = kvh * lay.k_mul + lay.k_add;
     const int nt_all = slot < 0 ? 0 : (kv_len - lo_al + AT_BN - 1) / AT_BN;
     const int per = (nt_all + n_splits - 1) / n_splits;
     const int t0 = split * per, t1 = min(nt_all, t0 + per);
@@ -326,7 +367,7 @@ decode_splitkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_poo
     for (int i = threadIdx.x; i < 16 * (D / 8); i += AT_THREADS) {
         const int r = i / (D / 8), c = i % (D / 8);
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < grp) v = *reinterpret_cast<const uint4*>(q + ((size_t)b * n_q + kvh * grp + r) * D + c * 8);
+        if (r < grp) v = *reinterpret_cast<const uint4*>(q + (size_t)b * lay.q_ts + (size_t)(kvh * grp + r) * lay.q_hs + lay.q_o + c * 8);
         *reinterpret_cast<uint4*>(sQ + r * LD + c * 8) = v;
     }
 
@@ -341,16 +382,26 @@ decode_splitkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_poo
             long long off[16 * CH / 32];
 #pragma unroll
             for (int p = 0; p < 16 * CH / 32; ++p)
-                off[p] = kv_row_offset(bt_row, key0 + (lane + p * 32) / CH, kv_len, n_kv, kvh, page_size, max_pages,
+                off[p] = kv_row_offset(bt_row, key0 + (lane + p * 32) / CH, kv_len, n_kh, kh, page_size, max_pages,
                                        n_pool_pages, D);
 #pragma unroll
             for (int p = 0; p < 16 * CH / 32; ++p) {
                 const int idx = lane + p * 32;
                 const int r = idx / CH, c = idx % CH;
                 const bool valid = off[p] >= 0;
-                const size_t o = valid ? (size_t)off[p] + c * 8 : 0;
-                cp_async_16(st + r * LD + c * 8, k_pool + o, valid);
-                cp_async_16(st + 16 * LD + r * LD + c * 8, v_pool + o, valid);
+                cp_async_16(st + r * LD + c * 8, k_pool + (valid ? (size_t)off[p] + c * 8 : 0), valid);
+            }
+            long long offv[16 * CHV / 32];
+#pragma unroll
+            for (int p = 0; p < 16 * CHV / 32; ++p)
+                offv[p] = kv_row_offset(bt_row, key0 + (lane + p * 32) / CHV, kv_len, n_kv, kvh, page_size, max_pages,
+                                        n_pool_pages, DV);
+#pragma unroll
+            for (int p = 0; p < 16 * CHV / 32; ++p) {
+                const int idx = lane + p * 32;
+                const int r = idx / CHV, c = idx % CHV;
+                const bool valid = offv[p] >= 0;
+                cp_async_16(st + 16 * LD + r * LDV + c * 8, v_pool + (valid ? (size_t)offv[p] + c * 8 : 0), valid);
             }
         }
         cp_async_commit();                                       // an empty group when nothing is left: the count stays uniform
@@ -359,9 +410,9 @@ decode_splitkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_poo
     for (int i = 0; i < AT_DEC_DEPTH - 1; ++i) issue(i);
 
     uint32_t a[D / 16][4];
-    float o[D / 8][4];
+    float o[DV / 8][4];
 #pragma unroll
-    for (int dt = 0; dt < D / 8; ++dt)
+    for (int dt = 0; dt < DV / 8; ++dt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[dt][e] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
@@ -385,8 +436,8 @@ decode_splitkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_poo
                     s[nt][e] = (j <= pos && j >= lo) ? s[nt][e] * scale_log2 : -INFINITY;
                 }
             uint32_t pf[1][4];
-            softmax_update<D, 2>(s, m, l, o, pf);
-            pv_product<D, 1>(o, pf, st + 16 * LD, 0);
+            softmax_update<DV, 2>(s, m, l, o, pf);
+            pv_product<DV, 1>(o, pf, st + 16 * LD, 0);
         }
         __syncwarp();                                            // the stage may be overwritten by the next issue
     }
@@ -398,22 +449,22 @@ decode_splitkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_poo
     }
     __syncthreads();                                             // all warps are done with their queues
     // merge the four warps (each saw other keys) through shared memory, reusing the tile buffers
-    float* mO = reinterpret_cast<float*>(sKV);                   // [4][16][D]
-    float* mM = mO + 4 * 16 * D;                                 // [4][16]
+    float* mO = reinterpret_cast<float*>(sKV);                   // [4][16][DV]
+    float* mM = mO + 4 * 16 * DV;                                // [4][16]
     float* mL = mM + 4 * 16;                                     // [4][16]
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
         const int r = g + hh * 8;
 #pragma unroll
-        for (int dt = 0; dt < D / 8; ++dt) {
-            mO[(warp * 16 + r) * D + dt * 8 + 2 * t] = o[dt][hh * 2];
-            mO[(warp * 16 + r) * D + dt * 8 + 2 * t + 1] = o[dt][hh * 2 + 1];
+        for (int dt = 0; dt < DV / 8; ++dt) {
+            mO[(warp * 16 + r) * DV + dt * 8 + 2 * t] = o[dt][hh * 2];
+            mO[(warp * 16 + r) * DV + dt * 8 + 2 * t + 1] = o[dt][hh * 2 + 1];
         }
         if (t == 0) { mM[warp * 16 + r] = m[hh]; mL[warp * 16 + r] = l[hh]; }
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < grp * D; i += AT_THREADS) {
-        const int r = i / D, dim = i % D;
+    for (int i = threadIdx.x; i < grp * DV; i += AT_THREADS) {
+        const int r = i / DV, dim = i % DV;
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < 4; ++w) M = fmaxf(M, mM[w * 16 + r]);
@@ -422,11 +473,11 @@ decode_splitkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_poo
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
                 const float f = exp2f(mM[w * 16 + r] - M);       // 0 for a warp that saw no key
-                acc += f * mO[(w * 16 + r) * D + dim];
+                acc += f * mO[(w * 16 + r) * DV + dim];
                 L += f * mL[w * 16 + r];
             }
         }
-        part_o[(((size_t)b * n_q + kvh * grp + r) * n_splits + split) * D + dim] = acc;
+        part_o[(((size_t)b * n_q + kvh * grp + r) * n_splits + split) * DV + dim] = acc;
         if (dim == 0) {
             my_ml[(size_t)r * n_splits * 2] = M;
             my_ml[(size_t)r * n_splits * 2 + 1] = L;
@@ -437,9 +488,11 @@ decode_splitkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_poo
 template <int D>
 __global__ void __launch_bounds__(128)
 decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out,
-                      int n_splits) {
+                      int n_splits, int n_q, long long o_ts, long long o_hs, long long o_o) {
     gi_pdl_start();
     const size_t row = blockIdx.x;                               // sequence * n_q + head
+    // where the row's result goes: dense rows, or (n_q > 0) sequence * o_ts + head * o_hs + o_o
+    bf16* dst = n_q > 0 ? out + (row / n_q) * o_ts + (row % n_q) * o_hs + o_o : out + row * D;
     const float* ml = part_ml + row * n_splits * 2;
     float M = -INFINITY;
     for (int s = 0; s < n_splits; ++s) M = fmaxf(M, ml[2 * s]);
@@ -454,7 +507,7 @@ decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict_
                 L += f * ml[2 * s + 1];
             }
         }
-        out[row * D + dim] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        dst[dim] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
     }
 }
 
@@ -472,6 +525,38 @@ decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict_
         default: GI_REQUIRE(false, "attention (tensor cores): head_dim %d must be a multiple of 16 up to 128", d); \
     }
 
+// Pairs (key size, value size) the kernels are built for: equal sizes, values twice the keys, keys twice the values;
+// multiples of 16 up to 128.
+#define AT_DISPATCH_DD(dk, dv, CALL)                                                                           \
+    if ((dk) == (dv)) {                                                                                        \
+        switch (dk) {                                                                                          \
+            case 16: { CALL(16, 16); break; }   case 32: { CALL(32, 32); break; }                              \
+            case 48: { CALL(48, 48); break; }   case 64: { CALL(64, 64); break; }                              \
+            case 80: { CALL(80, 80); break; }   case 96: { CALL(96, 96); break; }                              \
+            case 112: { CALL(112, 112); break; } case 128: { CALL(128, 128); break; }                          \
+            default: GI_REQUIRE(false, "attention (tensor cores): head_dim %d must be a multiple of 16 up to 128", dk); \
+        }                                                                                                      \
+    } else if ((dv) == 2 * (dk)) {                                                                             \
+        switch (dk) {                                                                                          \
+            case 16: { CALL(16, 32); break; }   case 32: { CALL(32, 64); break; }                              \
+            case 48: { CALL(48, 96); break; }   case 64: { CALL(64, 128); break; }                             \
+            default: GI_REQUIRE(false, "attention (tensor cores): keys of %d with values of %d", dk, dv);      \
+        }                                                                                                      \
+    } else if ((dk) == 2 * (dv)) {                                                                             \
+        switch (dv) {                                                                                          \
+            case 16: { CALL(32, 16); break; }   case 32: { CALL(64, 32); break; }                              \
+            case 48: { CALL(96, 48); break; }   case 64: { CALL(128, 64); break; }                             \
+            default: GI_REQUIRE(false, "attention (tensor cores): keys of %d with values of %d", dk, dv);      \
+        }                                                                                                      \
+    } else {                                                                                                   \
+        GI_REQUIRE(false, "attention (tensor cores): keys of %d with values of %d", dk, dv);                   \
+    }
+
+extern "C" int gi_attention_mma_takes(int dk, int dv) {
+    const bool ok16 = dk > 0 && dv > 0 && dk % 16 == 0 && dv % 16 == 0 && dk <= 128 && dv <= 128;
+    return ok16 && (dk == dv || dv == 2 * dk || dk == 2 * dv);
+}
+
 static int check_common(const char* who, int n_q, int n_kv, int d, int page_size, int max_pages, int window) {
     GI_REQUIRE(n_q > 0 && n_kv > 0 && n_q % n_kv == 0, "%s: %d query heads are no multiple of %d key/value heads", who, n_q, n_kv);
     GI_REQUIRE(d > 0 && d % 16 == 0 && d <= 128, "%s: head_dim %d must be a multiple of 16 up to 128", who, d);
@@ -480,30 +565,99 @@ static int check_common(const char* who, int n_q, int n_kv, int d, int page_size
 }
 
 // Raises a kernel's dynamic shared memory limit, once per kernel and device.
-template <int D, int WHICH>
 static int set_smem(const void* kernel, size_t bytes) { return gi_reserve_smem(kernel, bytes, "attention"); }
+
+static AttnLayout plain_layout(int n_q, int d, int dv) {
+    AttnLayout lay;
+    lay.q_ts = (long long)n_q * d; lay.q_hs = d; lay.q_o = 0;
+    lay.o_ts = (long long)n_q * dv; lay.o_hs = dv; lay.o_o = 0;
+    lay.n_kh = 0; lay.k_mul = 1; lay.k_add = 0; lay.chunk = 0;
+    return lay;
+}
+
+// Map m of `maps` per head: q [rows, n_q, maps, d], out [rows, n_q, maps, dv], key pool [pages, n_kv * maps, page, d].
+static AttnLayout map_layout(int n_q, int n_kv, int d, int dv, int maps, int m, int chunk) {
+    AttnLayout lay;
+    lay.q_ts = (long long)n_q * maps * d; lay.q_hs = (long long)maps * d; lay.q_o = (long long)m * d;
+    lay.o_ts = (long long)n_q * maps * dv; lay.o_hs = (long long)maps * dv; lay.o_o = (long long)m * dv;
+    lay.n_kh = n_kv * maps; lay.k_mul = maps; lay.k_add = m; lay.chunk = chunk;
+    return lay;
+}
+
+static int prefill_bf16_layout(const void* q, const void* k_pool, const void* v_pool, const int* block_table,
+                               const int* tiles, int n_tiles, void* out, int n_q, int n_kv, int d, int dv,
+                               int page_size, int max_pages, int n_pool_pages, int window, float scale,
+                               AttnLayout lay, void* stream) {
+    if (int rc = check_common("gi_attention_prefill_bf16", n_q, n_kv, d, page_size, max_pages, window)) return rc;
+    GI_REQUIRE(n_tiles >= 0 && n_q <= 65535, "gi_attention_prefill_bf16: tile or head count");
+    if (n_tiles == 0) return 0;
+    const float scale_log2 = scale * 1.4426950408889634f;
+    dim3 grid(n_tiles, n_q);
+#define CALL(DK, DV)                                                                                           \
+    {                                                                                                          \
+        const size_t smem = ((size_t)(AT_BM + 2 * AT_BN) * (DK + 8) + (size_t)2 * AT_BN * (DV + 8)) * sizeof(bf16); \
+        if (int rc = set_smem((const void*)flash_prefill_kernel<DK, DV>, smem)) return rc;                     \
+        gi_launch(flash_prefill_kernel<DK, DV>, grid, dim3(AT_THREADS), smem, (cudaStream_t)stream,            \
+            (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table, (const int4*)tiles,         \
+            (bf16*)out, n_q, n_kv, page_size, max_pages, n_pool_pages, window, scale_log2, lay);               \
+    }
+    AT_DISPATCH_DD(d, dv, CALL)
+#undef CALL
+    return gi_check_launch("gi_attention_prefill_bf16");
+}
 
 // tiles: int32 [n_tiles, 4] = {slot, first q row, rows (<= 64), position of the first row}
 extern "C" int gi_attention_prefill_bf16(const void* q, const void* k_pool, const void* v_pool, const int* block_table,
                                          const int* tiles, int n_tiles, void* out, int n_q, int n_kv, int d,
                                          int page_size, int max_pages, int n_pool_pages, int window, float scale,
                                          void* stream) {
-    if (int rc = check_common("gi_attention_prefill_bf16", n_q, n_kv, d, page_size, max_pages, window)) return rc;
-    GI_REQUIRE(n_tiles >= 0 && n_q <= 65535, "gi_attention_prefill_bf16: tile or head count");
-    if (n_tiles == 0) return 0;
+    return prefill_bf16_layout(q, k_pool, v_pool, block_table, tiles, n_tiles, out, n_q, n_kv, d, d, page_size, max_pages,
+                               n_pool_pages, window, scale, plain_layout(n_q, d, d), stream);
+}
+
+// The general prompt kernel: keys of d and values of dv, `maps` softmax maps per head over the same values (q
+// [rows, n_q, maps, d], out [rows, n_q, maps, dv], the key pool [pages, n_kv * maps, page, d]: one launch per map),
+// and `chunk` (0: none).
+extern "C" int gi_attention_prefill_masked_bf16(const void* q, const void* k_pool, const void* v_pool,
+                                                const int* block_table, const int* tiles, int n_tiles, void* out, int n_q,
+                                                int n_kv, int d, int dv, int page_size, int max_pages, int n_pool_pages,
+                                                int window, int chunk, int maps, float scale, void* stream) {
+    GI_REQUIRE(maps >= 1 && chunk >= 0, "gi_attention_prefill_masked_bf16: %d maps, chunk %d", maps, chunk);
+    for (int m = 0; m < maps; ++m)
+        if (int rc = prefill_bf16_layout(q, k_pool, v_pool, block_table, tiles, n_tiles, out, n_q, n_kv, d, dv, page_size,
+                                         max_pages, n_pool_pages, window, scale,
+                                         map_layout(n_q, n_kv, d, dv, maps, m, chunk), stream)) return rc;
+    return 0;
+}
+
+static int decode_bf16_layout(const void* q, const void* k_pool, const void* v_pool, const int* block_table,
+                              const int* tok_pos, const int* tok_slot, void* out, float* part_o, float* part_ml,
+                              int n_seqs, int n_q, int n_kv, int d, int dv, int page_size, int max_pages,
+                              int n_pool_pages, int window, float scale, int n_splits, AttnLayout lay, bool strided_out,
+                              void* stream) {
+    if (int rc = check_common("gi_attention_decode_bf16", n_q, n_kv, d, page_size, max_pages, window)) return rc;
+    GI_REQUIRE(n_q / n_kv <= 16, "gi_attention_decode_bf16: %d query heads per key/value head; this kernel takes up to 16", n_q / n_kv);
+    GI_REQUIRE(n_splits >= 1 && n_splits <= 65535 && n_kv <= 65535 && n_seqs >= 0 && n_seqs <= 65535,
+               "gi_attention_decode_bf16: %d slices, %d key/value heads, %d sequences", n_splits, n_kv, n_seqs);
+    if (n_seqs == 0) return 0;
     const float scale_log2 = scale * 1.4426950408889634f;
-    dim3 grid(n_tiles, n_q);
-#define CALL(DD)                                                                                               \
+    dim3 grid(n_splits, n_kv, n_seqs);
+    const int cq = strided_out ? n_q : 0;
+#define CALL(DK, DV)                                                                                           \
     {                                                                                                          \
-        const size_t smem = (size_t)(AT_BM + 4 * AT_BN) * (DD + 8) * sizeof(bf16);                             \
-        if (int rc = set_smem<DD, 0>((const void*)flash_prefill_kernel<DD>, smem)) return rc;                     \
-        gi_launch(flash_prefill_kernel<DD>, grid, dim3(AT_THREADS), smem, (cudaStream_t)stream,                             \
-            (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table, (const int4*)tiles,         \
-            (bf16*)out, n_q, n_kv, page_size, max_pages, n_pool_pages, window, scale_log2);                    \
+        size_t smem = ((size_t)16 * (DK + 8) + (size_t)4 * AT_DEC_DEPTH * 16 * (DK + 8 + DV + 8)) * sizeof(bf16); \
+        const size_t merge = (size_t)16 * (DK + 8) * sizeof(bf16) + (size_t)(4 * 16 * DV + 128) * sizeof(float); \
+        if (merge > smem) smem = merge;                                                                        \
+        if (int rc = set_smem((const void*)decode_splitkv_kernel<DK, DV>, smem)) return rc;                    \
+        gi_launch(decode_splitkv_kernel<DK, DV>, grid, dim3(AT_THREADS), smem, (cudaStream_t)stream,           \
+            (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table, tok_pos, tok_slot, part_o,  \
+            part_ml, n_q, n_kv, page_size, max_pages, n_pool_pages, window, scale_log2, n_splits, lay);        \
+        gi_launch(decode_combine_kernel<DV>, dim3(n_seqs * n_q), dim3(DV < 128 ? (DV < 32 ? 32 : DV) : 128), 0, (cudaStream_t)stream,  \
+            part_o, part_ml, (bf16*)out, n_splits, cq, lay.o_ts, lay.o_hs, lay.o_o);                           \
     }
-    AT_DISPATCH_D(d, CALL)
+    AT_DISPATCH_DD(d, dv, CALL)
 #undef CALL
-    return gi_check_launch("gi_attention_prefill_bf16");
+    return gi_check_launch("gi_attention_decode_bf16");
 }
 
 // Scratch: part_o float32 [n_seqs * n_q * n_splits * d], part_ml float32 [n_seqs * n_q * n_splits * 2].
@@ -512,28 +666,24 @@ extern "C" int gi_attention_decode_bf16(const void* q, const void* k_pool, const
                                         float* part_ml, int n_seqs, int n_q, int n_kv, int d, int page_size,
                                         int max_pages, int n_pool_pages, int window, float scale, int n_splits,
                                         void* stream) {
-    if (int rc = check_common("gi_attention_decode_bf16", n_q, n_kv, d, page_size, max_pages, window)) return rc;
-    GI_REQUIRE(n_q / n_kv <= 16, "gi_attention_decode_bf16: %d query heads per key/value head; this kernel takes up to 16", n_q / n_kv);
-    GI_REQUIRE(n_splits >= 1 && n_splits <= 65535 && n_kv <= 65535 && n_seqs >= 0 && n_seqs <= 65535,
-               "gi_attention_decode_bf16: %d slices, %d key/value heads, %d sequences", n_splits, n_kv, n_seqs);
-    if (n_seqs == 0) return 0;
-    const float scale_log2 = scale * 1.4426950408889634f;
-    dim3 grid(n_splits, n_kv, n_seqs);
-#define CALL(DD)                                                                                               \
-    {                                                                                                          \
-        size_t smem = (size_t)(16 + 4 * AT_DEC_DEPTH * 32) * (DD + 8) * sizeof(bf16);                          \
-        const size_t merge = (size_t)16 * (DD + 8) * sizeof(bf16) + (size_t)(4 * 16 * DD + 128) * sizeof(float); \
-        if (merge > smem) smem = merge;                                                                        \
-        if (int rc = set_smem<DD, 1>((const void*)decode_splitkv_kernel<DD>, smem)) return rc;                    \
-        gi_launch(decode_splitkv_kernel<DD>, grid, dim3(AT_THREADS), smem, (cudaStream_t)stream,                            \
-            (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table, tok_pos, tok_slot, part_o,  \
-            part_ml, n_q, n_kv, page_size, max_pages, n_pool_pages, window, scale_log2, n_splits);             \
-        gi_launch(decode_combine_kernel<DD>, dim3(n_seqs * n_q), dim3(DD < 128 ? (DD < 32 ? 32 : DD) : 128), 0, (cudaStream_t)stream,  \
-            part_o, part_ml, (bf16*)out, n_splits);                                                            \
-    }
-    AT_DISPATCH_D(d, CALL)
-#undef CALL
-    return gi_check_launch("gi_attention_decode_bf16");
+    return decode_bf16_layout(q, k_pool, v_pool, block_table, tok_pos, tok_slot, out, part_o, part_ml, n_seqs, n_q, n_kv,
+                              d, d, page_size, max_pages, n_pool_pages, window, scale, n_splits, plain_layout(n_q, d, d),
+                              false, stream);
+}
+
+// The general decode kernel: as gi_attention_prefill_masked_bf16, for one token per sequence.  Scratch as above with
+// dv for d (used by one map after the other).
+extern "C" int gi_attention_decode_masked_bf16(const void* q, const void* k_pool, const void* v_pool,
+                                               const int* block_table, const int* tok_pos, const int* tok_slot, void* out,
+                                               float* part_o, float* part_ml, int n_seqs, int n_q, int n_kv, int d, int dv,
+                                               int page_size, int max_pages, int n_pool_pages, int window, int chunk,
+                                               int maps, float scale, int n_splits, void* stream) {
+    GI_REQUIRE(maps >= 1 && chunk >= 0, "gi_attention_decode_masked_bf16: %d maps, chunk %d", maps, chunk);
+    for (int m = 0; m < maps; ++m)
+        if (int rc = decode_bf16_layout(q, k_pool, v_pool, block_table, tok_pos, tok_slot, out, part_o, part_ml, n_seqs,
+                                        n_q, n_kv, d, dv, page_size, max_pages, n_pool_pages, window, scale, n_splits,
+                                        map_layout(n_q, n_kv, d, dv, maps, m, chunk), true, stream)) return rc;
+    return 0;
 }
 
 // Merges the slices' partial results of a split-KV decode kernel (this file's or the tcgen05 one):
@@ -546,7 +696,7 @@ extern "C" int gi_attention_decode_combine(const float* part_o, const float* par
     if (rows == 0) return 0;
 #define CALL(DD)                                                                                                 \
     gi_launch(decode_combine_kernel<DD>, dim3(rows), dim3(DD < 128 ? (DD < 32 ? 32 : DD) : 128), 0, (cudaStream_t)stream, \
-              part_o, part_ml, (bf16*)out, n_splits);
+              part_o, part_ml, (bf16*)out, n_splits, 0, 0LL, 0LL, 0LL);
     AT_DISPATCH_D(d, CALL)
 #undef CALL
     return gi_check_launch("gi_attention_decode_combine");

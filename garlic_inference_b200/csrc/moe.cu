@@ -80,7 +80,24 @@ template <> __device__ __forceinline__ float dot_row<float>(const float* __restr
 template <> __device__ __forceinline__ float dot_row<bf16>(const bf16* __restrict__ w, const float* __restrict__ x, int k, int lane) {
     float s = 0.f;
     if (k % 8 == 0 && (uintptr_t)w % 16 == 0) {
-        for (int c = lane * 8; c < k; c += 256) {
+        // four 16-byte loads of a lane are asked for before any is used: the row is one stream of memory latencies
+        int c = lane * 8;
+        for (; c + 3 * 256 < k; c += 4 * 256) {
+            uint4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const uint4*>(w + c + u * 256);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __bfloat1622float2(p2[i]);
+                    s = fmaf(f.x, x[c + u * 256 + 2 * i], s);
+                    s = fmaf(f.y, x[c + u * 256 + 2 * i + 1], s);
+                }
+            }
+        }
+        for (; c < k; c += 256) {
             const uint4 v = *reinterpret_cast<const uint4*>(w + c);
             const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll

@@ -829,9 +829,13 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], streams: O
     return out
 
 
-def mma_attention_takes(dtype: torch.dtype, head_dim: int) -> bool:
-    """Whether the tensor-core attention kernels take this element type and head size."""
-    return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 128
+def mma_attention_takes(dtype: torch.dtype, head_dim: int, value_dim: Optional[int] = None) -> bool:
+    """Whether the tensor-core attention kernels take this element type and head size (with `value_dim`: keys of
+    `head_dim` and values of `value_dim`, which the general entry points take when one is twice the other)."""
+    if value_dim is None or value_dim == head_dim:
+        return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 128
+    from .library import lib
+    return dtype == torch.bfloat16 and bool(lib().gi_attention_mma_takes(int(head_dim), int(value_dim)))
 
 
 def attention_prefill_bf16(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
@@ -853,6 +857,61 @@ def attention_prefill_bf16(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
     check(l.gi_attention_prefill_bf16(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), _ptr(q_tiles),
                                       q_tiles.shape[0], _ptr(out), n_q, n_kv, d, page_size, block_table.shape[1],
                                       n_pages, int(window or 0), float(scale), _stream()), l)
+    return out
+
+
+def _masked_shapes(q, k_pool, v_pool, maps):
+    n, rows, d = q.shape
+    n_pages, n_kh, page_size, pool_d = k_pool.shape
+    n_kv, dv = v_pool.shape[1], v_pool.shape[3]
+    if rows % maps or n_kh != n_kv * maps or pool_d != d or tuple(v_pool.shape) != (n_pages, n_kv, page_size, dv):
+        raise KernelError(f"q {tuple(q.shape)}, keys {tuple(k_pool.shape)} and values {tuple(v_pool.shape)} do not fit "
+                          f"{maps} maps per head")
+    return n, rows, d, dv, n_pages, n_kv, page_size
+
+
+def attention_prefill_masked_bf16(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
+                                  q_tiles: torch.Tensor, scale: float, window: int = 0, chunk: int = 0, maps: int = 1,
+                                  rows_covered: bool = False) -> torch.Tensor:
+    """The tensor-core prompt kernel with a chunk mask, values of a size of their own and `maps` softmax maps per
+    head over the same values: q [n, heads * maps, d] (a head's maps side by side), keys [pages, key/value heads *
+    maps, page, d], values [pages, key/value heads, page, dv].  Returns [n, heads * maps * dv], a head's maps side
+    by side."""
+    l = require_gpu()
+    _dense(q, "q", torch.bfloat16), _dense(k_pool, "k_pool", torch.bfloat16), _dense(v_pool, "v_pool", torch.bfloat16)
+    _dense(block_table, "block_table", torch.int32), _dense(q_tiles, "q_tiles", torch.int32)
+    n, rows, d, dv, n_pages, n_kv, page_size = _masked_shapes(q, k_pool, v_pool, maps)
+    if q_tiles.dim() != 2 or q_tiles.shape[1] != 4 or q_tiles.data_ptr() % 16:
+        raise KernelError("q_tiles must be int32 [n_tiles, 4] starting on 16 bytes")
+    out = (torch.empty if rows_covered else torch.zeros)((n, rows * dv), dtype=q.dtype, device=q.device)
+    check(l.gi_attention_prefill_masked_bf16(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), _ptr(q_tiles),
+                                             q_tiles.shape[0], _ptr(out), rows // maps, n_kv, d, dv, page_size,
+                                             block_table.shape[1], n_pages, int(window or 0), int(chunk or 0), int(maps),
+                                             float(scale), _stream()), l)
+    counters.launches += maps - 1
+    return out
+
+
+def attention_decode_masked_bf16(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
+                                 tok_pos: torch.Tensor, tok_slot: torch.Tensor, scale: float, window: int = 0,
+                                 chunk: int = 0, maps: int = 1, n_splits: Optional[int] = None) -> torch.Tensor:
+    """The split-KV decode kernel with the same options: one token per sequence, q [n_seqs, heads * maps, d].
+    Returns [n_seqs, heads * maps * dv]."""
+    l = require_gpu()
+    _dense(q, "q", torch.bfloat16), _dense(k_pool, "k_pool", torch.bfloat16), _dense(v_pool, "v_pool", torch.bfloat16)
+    for t, name in ((tok_pos, "tok_pos"), (tok_slot, "tok_slot"), (block_table, "block_table")):
+        _dense(t, name, torch.int32)
+    n, rows, d, dv, n_pages, n_kv, page_size = _masked_shapes(q, k_pool, v_pool, maps)
+    heads = rows // maps
+    n_splits = n_splits or decode_splits(n, n_kv)
+    out = torch.empty((n, rows * dv), dtype=q.dtype, device=q.device)
+    part_o = torch.empty((n * heads * n_splits * dv,), dtype=torch.float32, device=q.device)
+    part_ml = torch.empty((n * heads * n_splits * 2,), dtype=torch.float32, device=q.device)
+    check(l.gi_attention_decode_masked_bf16(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), _ptr(tok_pos),
+                                            _ptr(tok_slot), _ptr(out), _ptr(part_o), _ptr(part_ml), n, heads, n_kv, d, dv,
+                                            page_size, block_table.shape[1], n_pages, int(window or 0), int(chunk or 0),
+                                            int(maps), float(scale), n_splits, _stream()), l)
+    counters.launches += 2 * maps - 1
     return out
 
 

@@ -56,6 +56,9 @@ _SIGNATURES = {
     "gi_latent_decode": ([P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, I, P, P], I),
     "gi_latent_prepare": ([P, L, I, I, P, I, P, I, F, P, F, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, P], I),
     "gi_attention_prefill_bf16": ([P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, P], I),
+    "gi_attention_prefill_masked_bf16": ([P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, I, I, F, P], I),
+    "gi_attention_decode_masked_bf16": ([P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, I, P], I),
+    "gi_attention_mma_takes": ([I, I], I),
     "gi_attention_prefill_tcgen05": ([P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, F, P, P], I),
     "gi_attention_decode_bf16": ([P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P], I),
     "gi_set_pdl": ([I], None),

@@ -18,9 +18,12 @@ Query head h reads key/value head h // (n_heads // n_kv_heads).  With `own_kv` F
 value tensors: the schedule points it at another layer's cache entry, whose keys and values (as that cache holds
 them: after convolution and rotation) it reads with its own queries, mask and everything else.
 
-All projections that read x are one packed product.  Scores, softmax and the weighted sums are float32 (the
-exact-order kernel: a position's result does not depend on how the tokens were cut into steps); what comes out
-of it is combined, normed and gated in float32 and rounded once.  Upstream has grouped-query attention only
+All projections that read x are one packed product.  Which attention runs: in bfloat16, with key and value
+sizes that the tensor-core kernels take (multiples of 16 up to 128, equal or one twice the other): the flash
+kernel for steps that bring several tokens of a sequence and the split-KV kernel for decode steps, once per map,
+with the chunk mask in them (float32 scores, softmax and sums; the weights rounded to bfloat16 as the second
+product's operand).  Everything else (float32, other sizes): the exact-order kernel, whose result at a position does not depend on how the tokens were cut into steps.  What
+comes out is combined, normed and gated in float32 and rounded once.  Upstream has grouped-query attention only
 (src/models/qwen3/qwen3.cpp:140-179).
 """
 from __future__ import annotations
@@ -30,6 +33,7 @@ import torch
 from ..cache import EntryRequirement, KVRequirement, StateRequirement
 from ..ops import kernels, linear
 from ..weights.loader import TensorWant
+from .attention import query_runs
 from .base import Mixer, register_part
 from .linear_attention import pack_rows
 
@@ -106,6 +110,14 @@ class MaskedAttention(Mixer):
             return kv
         return EntryRequirement(kv, StateRequirement((self.state_floats,), torch.float32))
 
+    def _tensor_cores(self) -> bool:
+        return kernels.mma_attention_takes(self.rt.dtype, self.d, self.dv)
+
+    def step_arrays(self, shape, cache):
+        if shape.all_single or not self._tensor_cores():
+            return {}
+        return {"query_runs_64": lambda: query_runs(shape, 64)}
+
     def _rotation(self, position):
         if position is None:
             return None, 0, False
@@ -141,9 +153,20 @@ class MaskedAttention(Mixer):
         q = kernels.attn_prepare(src, 0, self.Cq if self.own_kv else -1, self.Cq + self.Ck, freq, n_rot, half,
                                  ctx.tok_pos, ctx.tok_slot, kv.block_table, kv.k_pool, kv.v_pool, self.H * self.maps,
                                  self.d, self.rt.dtype, ctx.status, append=writes_cache)
-        att = kernels.attention_masked(q, kv.k_pool, kv.v_pool, kv.block_table, ctx.tok_pos, ctx.tok_slot, self.scale,
-                                       ctx.status, window=self.window, chunk=self.chunk, maps=self.maps,
-                                       out_float32=True)
+        if ctx.all_single and self._tensor_cores() and self.H // self.G <= 16:
+            att = kernels.attention_decode_masked_bf16(q, kv.k_pool, kv.v_pool, kv.block_table, ctx.tok_pos, ctx.tok_slot,
+                                                       self.scale, window=self.window, chunk=self.chunk, maps=self.maps)
+        elif not ctx.all_single and ctx.seq_lens and self._tensor_cores():
+            runs = ctx.arrays.get("query_runs_64")
+            if runs is None:                      # a context put together by hand: cut and copy here
+                runs = ctx.arrays["query_runs_64"] = torch.from_numpy(query_runs(ctx, 64)).to(x.device)
+            att = kernels.attention_prefill_masked_bf16(q, kv.k_pool, kv.v_pool, kv.block_table, runs, self.scale,
+                                                        window=self.window, chunk=self.chunk, maps=self.maps,
+                                                        rows_covered=ctx.n_tokens == sum(ctx.seq_lens))
+        else:
+            att = kernels.attention_masked(q, kv.k_pool, kv.v_pool, kv.block_table, ctx.tok_pos, ctx.tok_slot,
+                                           self.scale, ctx.status, window=self.window, chunk=self.chunk,
+                                           maps=self.maps, out_float32=True)
         gate = proj[:, self.g_off:self.g_off + self.H] if self.head_gate else None
         return kernels.attn_finish(att, self.H, self.maps, self.lam, self.sub_norm_eps, self.out_mul, gate, self.rt.dtype)
 

@@ -302,8 +302,8 @@ def test_kernels_refuse_what_they_cannot_take():
     pool = torch.zeros(4, 2, 16, 20, dtype=torch.float32, device=DEV)
     bt = torch.zeros(1, 4, dtype=torch.int32, device=DEV)
     z = torch.zeros(2, dtype=torch.int32, device=DEV)
-    with pytest.raises(KernelError, match="multiple of 8"):
-        K().attention_generic(q, pool, pool, bt, z, z, 1.0, 0, z[:1])
+    with pytest.raises(KernelError, match="value columns"):
+        K().attention_generic(q, pool, pool, bt, z, z, 1.0, 0, z[:1], value_dim=24)
 
 
 # ------------------------------------------------------------------ cache write + attention

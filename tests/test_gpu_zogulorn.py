@@ -339,6 +339,49 @@ def test_rotation_append_and_masked_attention_kernels():
     assert int(status.item()) == 0
 
 
+@pytest.mark.parametrize("d,dv", [(32, 32), (16, 32), (64, 32), (96, 96)])
+def test_tensor_core_attention_with_chunks_two_maps_and_values_of_another_size(d, dv):
+    """The tensor-core kernels (bfloat16) with a chunk mask, two maps per head and values of a size of their own:
+    the prompt kernel for two sequences of unequal lengths of which one goes on from cached keys, and the decode
+    kernel for the last token of each."""
+    from garlic_inference_b200.ops import kernels
+    from garlic_inference_b200.parts import StepShape
+    from garlic_inference_b200.parts.attention import query_runs
+    torch.manual_seed(4)
+    H, G, page, maps, chunk = 4, 2, 16, 2, 50
+    lens, past = [150, 70], [0, 90]
+    n_pages = 24
+    k_pool = (torch.randn(n_pages, G * maps, page, d, device="cuda") * 0.7).bfloat16()
+    v_pool = torch.randn(n_pages, G, page, dv, device="cuda").bfloat16()
+    table = torch.full((2, 12), -1, dtype=torch.int32, device="cuda")
+    table[0, :10] = torch.arange(10, dtype=torch.int32) * 2 + 1
+    table[1, :10] = torch.arange(10, dtype=torch.int32) * 2
+    n = sum(lens)
+    q = torch.randn(n, H * maps, d, device="cuda").bfloat16()
+    runs = torch.from_numpy(query_runs(StepShape([0, 1], [0, 150], lens, past, False), 64)).cuda()
+    last = torch.tensor([149, 150 + 69], device="cuda")
+    pos1 = torch.tensor([149, 159], dtype=torch.int32, device="cuda")
+    slot1 = torch.tensor([0, 1], dtype=torch.int32, device="cuda")
+    for ch, win in ((chunk, 0), (0, 0), (7, 0), (0, 40)):
+        got = kernels.attention_prefill_masked_bf16(q, k_pool, v_pool, table, runs, 0.2, window=win, chunk=ch, maps=maps,
+                                                    rows_covered=True).float().cpu().view(n, H, maps, dv)
+        one = kernels.attention_decode_masked_bf16(q[last].contiguous(), k_pool, v_pool, table, pos1, slot1, 0.2, window=win,
+                                                   chunk=ch, maps=maps, n_splits=3).float().cpu().view(2, H, maps, dv)
+        for s, (start, m, p0) in enumerate(zip([0, 150], lens, past)):
+            T = p0 + m
+            pages = table[s, :-(-T // page)].long()
+            keys = k_pool[pages].float().cpu().permute(0, 2, 1, 3).reshape(-1, G, maps, d)[:T]
+            vals = v_pool[pages].float().cpu().permute(0, 2, 1, 3).reshape(-1, G, dv)[:T]
+            i, j = torch.arange(T)[:, None], torch.arange(T)[None, :]
+            seen = plain.chunk_mask(T, ch) if ch else ((j <= i) & (j > i - win) if win else j <= i)
+            qs = torch.zeros(T, H, maps, d)
+            qs[p0:] = q[start:start + m].float().cpu().view(m, H, maps, d)
+            for mp in range(maps):
+                want = plain.attend(qs[:, :, mp], keys[:, :, mp], vals, 0.2, seen)[p0:]
+                torch.testing.assert_close(got[start:start + m, :, mp], want, rtol=2e-2, atol=2e-2)
+                torch.testing.assert_close(one[s, :, mp], want[-1], rtol=2e-2, atol=2e-2)
+
+
 def test_delta_scan_with_a_decay_per_key_channel_and_plain_filters():
     from garlic_inference_b200.ops import kernels
     from garlic_inference_b200.parts.linear_attention import scan_state_floats

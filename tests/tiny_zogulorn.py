@@ -58,7 +58,7 @@ TINY = {
     "diff": dict(vocab=300, width=64, eps=1e-6, emb=3.0, seed=23, std=0.08, norm_std=0.1,
                  layers=[_with(_attention(3, 3, 24, 40, 20, 3, diff=0.3))]),
     "dense": dict(vocab=280, width=48, eps=1e-5, emb=1.0, seed=24, std=0.1, norm_std=0.1,
-                  layers=[_with(_attention(2, 1, 16, 8, 7, 2), _dense(100))]),
+                  layers=[_with(_attention(2, 1, 16, 16, 7, 2), _dense(100))]),
     "moe": dict(vocab=280, width=48, eps=1e-5, emb=5.0, seed=25, std=0.1, norm_std=0.1,
                 layers=[_with(_attention(2, 2, 8, 16, 64, 4, diff=0.7), _moe(40, 5, 2))]),
     # everything, in another order than any other configuration's; two layers on an earlier layer's keys and values
