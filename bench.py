@@ -696,6 +696,8 @@ def study_zogulorn(args, pk) -> int:
     # chunked attention for a prompt: the design's kernel, and the closest kernels (causal over all keys)
     ms = timed(lambda: kernels.attention_prefill_masked_bf16(q, kp, vp, table, runs64, 0.088, chunk=chunk, rows_covered=True))
     note("chunk_attention_prefill2048_mma", ms, flops=4.0 * H * d * seen)
+    ms = timed(lambda: kernels.attention_prefill_tcgen05(q, kp, vp, table, runs128, 0.088, 0, rows_covered=True, chunk=chunk))
+    note("chunk_attention_prefill2048_tcgen05", ms, flops=4.0 * H * d * seen)
     ms = timed(lambda: kernels.attention_prefill_bf16(q, kp, vp, table, runs64, 0.088, 0, rows_covered=True))
     note("gqa_attention_prefill2048_mma", ms, flops=4.0 * H * d * T * (T + 1) / 2)
     ms = timed(lambda: kernels.attention_prefill_tcgen05(q, kp, vp, table, runs128, 0.088, 0, rows_covered=True))
@@ -705,19 +707,25 @@ def study_zogulorn(args, pk) -> int:
     kpd, qd2 = bf(8 * T // page, Gd * 2, page, dd), bf(T, Hd * 2, dd)
     vpd = bf(8 * T // page, Gd, page, d)
     seen2 = sum(min(p % (2 * chunk), p) + 1 for p in range(T))
+    ms = timed(lambda: kernels.attention_prefill_masked_bf16(qd2, kpd, vpd, table, runs64, 0.125, chunk=2 * chunk, maps=2,
+                                                             rows_covered=True))
+    note("differential_attention_prefill2048_mma", ms, flops=2.0 * Hd * 2 * (dd + d) * seen2)
     ms = timed(lambda: kernels.attention_masked(qd2, kpd, vpd, table, pos, slot0, 0.125, status, chunk=2 * chunk, maps=2,
                                                 out_float32=True), reps=3, warm=1)
     note("differential_attention_prefill2048_exact_order", ms, flops=2.0 * Hd * 2 * (dd + d) * seen2)
     # decode steps: 8 sequences of 2,048 cached tokens
     q8 = bf(8, H, d)
+    ms = timed(lambda: kernels.attention_decode_masked_bf16(q8, kp, vp, table, pos8, slots8, 0.088, chunk=chunk))
+    note("chunk_attention_decode_b8_mma", ms, bytes_=8 * (T - chunk) * 2 * G * d * 2)
+    ms = timed(lambda: kernels.attention_decode_bf16(q8, kp, vp, table, pos8, slots8, 0.088, 0))
+    note("gqa_attention_decode_b8_mma", ms, bytes_=8 * T * 2 * G * d * 2)
     ms = timed(lambda: kernels.attention_masked(q8, kp, vp, table, pos8, slots8, 0.088, status, chunk=chunk, out_float32=True))
     note("chunk_attention_decode_b8_exact_order", ms, bytes_=8 * (T - chunk) * 2 * G * d * 2)
     ms = timed(lambda: kernels.attention_decode_tcgen05(q8, kp, vp, table, pos8, slots8, 0.088, 0))
     note("gqa_attention_decode_b8_tcgen05", ms, bytes_=8 * T * 2 * G * d * 2)
     q8d = bf(8, Hd * 2, dd)
-    ms = timed(lambda: kernels.attention_masked(q8d, kpd, vpd, table, pos8, slots8, 0.125, status, chunk=2 * chunk, maps=2,
-                                                out_float32=True))
-    note("differential_attention_decode_b8_exact_order", ms, bytes_=8 * T * (2 * Gd * dd + Gd * d) * 2)
+    ms = timed(lambda: kernels.attention_decode_masked_bf16(q8d, kpd, vpd, table, pos8, slots8, 0.125, chunk=2 * chunk, maps=2))
+    note("differential_attention_decode_b8_mma", ms, bytes_=8 * T * (2 * Gd * dd + Gd * d) * 2)
     # the delta rule's scan with a decay per key channel, beside the one with a decay per head
     Hr, Hk = 16, 8
     sf = Hr * scan_state_floats(d, d)
@@ -766,14 +774,14 @@ def study_zogulorn(args, pk) -> int:
     part = part_class("routed_experts")(dict(hidden_size=width, expert_size=eff, n_experts=E, top=top), Load(),
                                         Runtime(torch.bfloat16, torch.device(dev)))
     z = i32([0])
-    for n_rows in (8, T):
+    for n_rows in (1, 8, 64, T):
         x = bf(n_rows, width)
         ctx = StepContext(n_rows, z, z, z)
         ms = timed(lambda: part.step(x, ctx))
         active = min(E, n_rows * top) * 2 * eff * width * 2
         note(f"routed_experts_{n_rows}_rows", ms, flops=4.0 * n_rows * top * eff * width, bytes_=active)
     wgu, wd = bf(2 * 18432, width) * 0.05, bf(width, 18432) * 0.05
-    for n_rows in (8, T):
+    for n_rows in (1, 8, 64, T):
         x = bf(n_rows, width)
         ms = timed(lambda: linear(kernels.glu(linear(x, wgu), "gelu_tanh"), wd))
         note(f"dense_gelu_glu_ff_{n_rows}_rows", ms, flops=6.0 * n_rows * 18432 * width, bytes_=3 * 18432 * width * 2)

@@ -157,7 +157,7 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
                              const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
                              const int4* __restrict__ tiles, int n_q_tiles, bf16* __restrict__ out, int n_q, int n_kv,
                              int page_size, int max_pages, int n_pool_pages, int window, float scale_log2,
-                             int* __restrict__ error_flag) {
+                             int* __restrict__ error_flag, int chunk) {
     gi_pdl_start();
     extern __shared__ unsigned char ft_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)ft_raw + 1023) & ~(uintptr_t)1023);
@@ -178,7 +178,8 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
         it.slot = ti.x, it.row0 = ti.y, it.n_rows = ti.z, it.pos0 = ti.w;
         it.h = (int)(t % n_q), it.kvh = it.h / (n_q / n_kv);
         const int hi = it.pos0 + it.n_rows - 1;
-        const int lo = window > 0 ? max(0, it.pos0 - window + 1) : 0;
+        int lo = window > 0 ? max(0, it.pos0 - window + 1) : 0;
+        if (chunk > 0) lo = max(lo, it.pos0 / chunk * chunk);        // chunks of positions: a query sees its own chunk only
         it.kt_lo = lo / FT_BN;
         it.n_tiles = (it.slot < 0 || it.n_rows <= 0) ? 0 : hi / FT_BN - it.kt_lo + 1;
         return it.n_tiles > 0 ? 1 : 0;
@@ -354,11 +355,13 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
                     for (int j = 0; j < 32; ++j) { s[j] = a[j]; s[32 + j] = c2[j]; }
                 }
                 // tiles that every row of the CTA sees whole need no mask
-                if (key0 + FT_BN - 1 > im.pos0 || (window > 0 && key0 <= im.pos0 + FT_BM - 1 - window)) {
+                if (key0 + FT_BN - 1 > im.pos0 || (window > 0 && key0 <= im.pos0 + FT_BM - 1 - window) ||
+                    (chunk > 0 && key0 < (im.pos0 + FT_BM - 1) / chunk * chunk)) {
+                    const int first = chunk > 0 ? pos / chunk * chunk : 0;
 #pragma unroll
                     for (int j = 0; j < FT_BN; ++j) {
                         const int key = key0 + j;
-                        const bool seen = key <= pos && (window <= 0 || key > pos - window);
+                        const bool seen = key <= pos && (window <= 0 || key > pos - window) && key >= first;
                         s[j] = seen ? s[j] : -INFINITY;
                     }
                 }
@@ -478,11 +481,13 @@ static int ft_make_map(CUtensorMap* map, const void* base, long long rows, long 
 }
 
 // tiles: int32 [n_tiles, 4] = {slot, first q row, rows (<= 128), position of the first row}.
+// chunk > 0: a query sees only the keys of its own chunk of positions (chunks counted from position 0).
 // Takes head_dim 128 and page sizes that are a multiple of 64; everything else is refused.
 extern "C" int gi_attention_prefill_tcgen05(const void* q, const void* k_pool, const void* v_pool, const int* block_table,
                                             const int* tiles, int n_tiles, void* out, int n_tokens, int n_q, int n_kv,
                                             int d, int page_size, int max_pages, int n_pool_pages, int window,
-                                            float scale, int* error_flag, void* stream) {
+                                            int chunk, float scale, int* error_flag, void* stream) {
+    GI_REQUIRE(chunk >= 0, "gi_attention_prefill_tcgen05: chunk %d", chunk);
     GI_REQUIRE(d == FT_D, "gi_attention_prefill_tcgen05: head_dim %d; this kernel takes 128", d);
     GI_REQUIRE(page_size > 0 && page_size % FT_BN == 0, "gi_attention_prefill_tcgen05: page size %d is no multiple of 64", page_size);
     GI_REQUIRE(n_q > 0 && n_kv > 0 && n_q % n_kv == 0 && n_q <= 65535, "gi_attention_prefill_tcgen05: %d query heads, %d key/value heads", n_q, n_kv);
@@ -507,6 +512,6 @@ extern "C" int gi_attention_prefill_tcgen05(const void* q, const void* k_pool, c
     const long long grid = items < 2LL * n_sm ? items : 2LL * n_sm;      // two CTAs fit an SM
     gi_launch(flash_prefill_tcgen05_kernel, dim3((unsigned)grid), dim3(FT_THREADS), smem, (cudaStream_t)stream, map_q, map_k,
               map_v, block_table, (const int4*)tiles, n_tiles, (bf16*)out, n_q, n_kv, page_size, max_pages, n_pool_pages,
-              window, scale * 1.4426950408889634f, error_flag);
+              window, scale * 1.4426950408889634f, error_flag, chunk);
     return gi_check_launch("gi_attention_prefill_tcgen05");
 }

@@ -185,12 +185,14 @@ extern "C" int gi_xielu(const void* z, long long ldz, void* out, int act_dtype, 
 }
 
 // ------------------------------------------------------------------ group norm and gate of a read-out
-// o float32 [n, groups * gs]; one block per (row, group).  weight[c % w_len]: w_len = gs (one weight for all
+// o float32 [n, groups * gs]; one block per (row, group); the result is also multiplied by `mul` and written to
+// rows that lie ld_out apart (columns of a wider matrix).  weight[c % w_len]: w_len = gs (one weight for all
 // groups) or groups * gs.  gate_kind 0: sigmoid(g), 1: silu(g); g has the columns of o, row stride ldg.
 template <typename T>
 __global__ void gated_group_rmsnorm_kernel(const float* __restrict__ o, const T* __restrict__ g, long long ldg,
                                            const void* __restrict__ weight, int w_dtype, int w_len,
-                                           T* __restrict__ out, int groups, int gs, float eps, int gate_kind) {
+                                           T* __restrict__ out, int groups, int gs, float eps, int gate_kind,
+                                           float mul, long long ld_out) {
     gi_pdl_start();
     __shared__ float red[33];
     const size_t r = blockIdx.x;
@@ -206,13 +208,14 @@ __global__ void gated_group_rmsnorm_kernel(const float* __restrict__ o, const T*
         const int col = grp * gs + c;
         const float z = to_f32(g[r * ldg + col]);
         const float gate = gate_kind == 0 ? sigmoid_f(z) : z * sigmoid_f(z);
-        out[r * (size_t)groups * gs + col] = from_f32<T>(orow[c] * inv * load_w(weight, w_dtype, col % w_len) * gate);
+        out[r * (size_t)ld_out + col] = from_f32<T>(orow[c] * inv * load_w(weight, w_dtype, col % w_len) * gate * mul);
     }
 }
 
 extern "C" int gi_gated_group_rmsnorm(const float* o, const void* g, long long ldg, const void* weight, int w_dtype,
                                       int w_len, void* out, int act_dtype, int n_rows, int groups, int gs, float eps,
-                                      int gate_kind, void* stream) {
+                                      int gate_kind, float mul, long long ld_out, void* stream) {
+    GI_REQUIRE(ld_out >= (long long)groups * gs, "gi_gated_group_rmsnorm: output rows shorter than the groups");
     GI_REQUIRE(n_rows >= 0 && groups > 0 && gs > 0 && groups <= 65535, "gi_gated_group_rmsnorm: sizes");
     GI_REQUIRE(w_len == gs || w_len == groups * gs, "gi_gated_group_rmsnorm: a weight of %d elements fits neither a "
                "group of %d nor the row of %d", w_len, gs, groups * gs);
@@ -222,10 +225,10 @@ extern "C" int gi_gated_group_rmsnorm(const float* o, const void* g, long long l
     cudaStream_t s = (cudaStream_t)stream;
     if (act_dtype == GI_DTYPE_F32)
         gi_launch(gated_group_rmsnorm_kernel<float>, dim3(n_rows, groups), dim3(threads), 0, s, o, (const float*)g, ldg,
-                  weight, w_dtype, w_len, (float*)out, groups, gs, eps, gate_kind);
+                  weight, w_dtype, w_len, (float*)out, groups, gs, eps, gate_kind, mul, ld_out);
     else if (act_dtype == GI_DTYPE_BF16)
         gi_launch(gated_group_rmsnorm_kernel<bf16>, dim3(n_rows, groups), dim3(threads), 0, s, o, (const bf16*)g, ldg,
-                  weight, w_dtype, w_len, (bf16*)out, groups, gs, eps, gate_kind);
+                  weight, w_dtype, w_len, (bf16*)out, groups, gs, eps, gate_kind, mul, ld_out);
     else
         GI_REQUIRE(false, "gi_gated_group_rmsnorm: activation dtype %d", act_dtype);
     return gi_check_launch("gi_gated_group_rmsnorm");

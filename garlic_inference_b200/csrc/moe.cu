@@ -1,12 +1,13 @@
 // A routed feed-forward: every token runs `top` of `experts` small feed-forwards and sums their results with
 // the router's weights.
 //
+//   gi_router_logits   z = W_r x in float32 (float32 weight, the token's vector widened)
 //   gi_router_topk     per token: the `top` largest of its float32 router logits (ties: the lower index), in
 //                      falling order, and the softmax over those chosen logits alone
 //   gi_moe_up          a[t, j, :] = act( W_up[e_tj] x_t )          act: the square of relu (0) or silu (1)
-//   gi_moe_down        y[t, :] = sum_j w_tj W_down[e_tj] a[t, j, :]                  j in the router's order
-//   gi_moe_combine     y[t, :] = sum_j w_tj buf[where[t, j], :]                      the same sum over rows that a
-//                      grouped product wrote expert by expert
+//   gi_moe_down        part[t, j, :] = W_down[e_tj] a[t, j, :]
+//   gi_moe_combine     y[t, :] = sum_j w_tj buf[where[t, j], :]   in the router's order of j: over gi_moe_down's
+//                      rows (where = none: row t top + j), or over rows that a grouped product wrote expert by expert
 //
 // gi_moe_up and gi_moe_down read only the chosen experts' weights and take the expert of a row from device
 // memory, so a recorded decode step replays them for other tokens.  They are products of one row with a matrix,
@@ -64,6 +65,7 @@ extern "C" int gi_router_topk(const float* logits, long long ld, int E, int top,
 }
 
 // ------------------------------------------------------------------ one row times a chosen expert's matrix
+// (dot_row below also serves the router's logits.)
 template <typename T> __device__ __forceinline__ float dot_row(const T* __restrict__ w, const float* __restrict__ x, int k, int lane);
 template <> __device__ __forceinline__ float dot_row<float>(const float* __restrict__ w, const float* __restrict__ x, int k, int lane) {
     float s = 0.f;
@@ -113,14 +115,58 @@ template <> __device__ __forceinline__ float dot_row<bf16>(const bf16* __restric
     return warp_sum(s);
 }
 
+// Router logits z[t, e] = sum_c w[e, c] x[t, c] in float32: the weight is float32, the token's vector is widened
+// into shared memory, a warp per expert.  The weight (experts x hidden floats) stays in L2 over the launch.
+template <typename T>
+__global__ void __launch_bounds__(256)
+router_logits_kernel(const T* __restrict__ x, long long ldx, const float* __restrict__ w, float* __restrict__ z,
+                     int E, int hidden) {
+    gi_pdl_start();
+    extern __shared__ float xs[];
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) xs[c] = to_f32(x[(size_t)t * ldx + c]);
+    __syncthreads();
+    for (int e = blockIdx.y * 8 + warp; e < min(E, (int)(blockIdx.y + 1) * 8); e += 8) {
+        const float v = dot_row<float>(w + (size_t)e * hidden, xs, hidden, lane);
+        if (lane == 0) z[(size_t)t * E + e] = v;
+    }
+}
+
+extern "C" int gi_router_logits(const void* x, long long ldx, int act_dtype, const float* w, float* z, int n_rows, int E,
+                                int hidden, void* stream) {
+    GI_REQUIRE(n_rows >= 0 && E > 0 && hidden > 0 && ldx >= hidden && (E + 7) / 8 <= 65535, "gi_router_logits: sizes");
+    if (n_rows == 0) return 0;
+    const size_t smem = (size_t)hidden * sizeof(float);
+    dim3 grid(n_rows, (E + 7) / 8);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (act_dtype == GI_DTYPE_F32) {
+        if (smem > 48 * 1024) { int rc = gi_reserve_smem((const void*)router_logits_kernel<float>, smem, "gi_router_logits"); if (rc) return rc; }
+        gi_launch(router_logits_kernel<float>, grid, dim3(256), smem, s, (const float*)x, ldx, w, z, E, hidden);
+    } else if (act_dtype == GI_DTYPE_BF16) {
+        if (smem > 48 * 1024) { int rc = gi_reserve_smem((const void*)router_logits_kernel<bf16>, smem, "gi_router_logits"); if (rc) return rc; }
+        gi_launch(router_logits_kernel<bf16>, grid, dim3(256), smem, s, (const bf16*)x, ldx, w, z, E, hidden);
+    } else {
+        GI_REQUIRE(false, "gi_router_logits: activation dtype %d", act_dtype);
+    }
+    return gi_check_launch("gi_router_logits");
+}
+
 #define MOE_WARPS 8
-#define MOE_ROWS 32          // rows of W per block
+#define MOE_ROWS 32          // rows of W per block, at most
+
+// Rows of W per block: 32 when that still makes a couple of thousand blocks, else 16 or 8 (one row per warp), so that
+// a step of one or two tokens still has enough loads in flight on every SM.
+static int moe_rows_per_block(int pairs, int n_out) {
+    for (int rows = MOE_ROWS; rows > MOE_WARPS; rows /= 2)
+        if ((long long)pairs * ((n_out + rows - 1) / rows) >= 2048) return rows;
+    return MOE_WARPS;
+}
 
 // x [n, ldx] (T), w_up [E, ff, hidden], idx [n, top] -> a [n, top, ff]
 template <typename T>
 __global__ void __launch_bounds__(MOE_WARPS * 32)
 moe_up_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ w_up, const int* __restrict__ idx,
-              T* __restrict__ a, int top, int E, int ff, int hidden, int act) {
+              T* __restrict__ a, int top, int E, int ff, int hidden, int act, int rows_pb) {
     gi_pdl_start();
     extern __shared__ float xs[];                   // hidden
     const int tj = blockIdx.x, t = tj / top;
@@ -129,70 +175,70 @@ moe_up_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ w_up
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) xs[c] = to_f32(x[(size_t)t * ldx + c]);
     __syncthreads();
     const bool ok = e >= 0 && e < E;
-    for (int f = blockIdx.y * MOE_ROWS + warp; f < min(ff, (int)(blockIdx.y + 1) * MOE_ROWS); f += MOE_WARPS) {
+    for (int f = blockIdx.y * rows_pb + warp; f < min(ff, (int)(blockIdx.y + 1) * rows_pb); f += MOE_WARPS) {
         float z = ok ? dot_row<T>(w_up + ((size_t)e * ff + f) * hidden, xs, hidden, lane) : 0.f;
         if (act == 0) { z = fmaxf(z, 0.f); z = z * z; } else { z = z / (1.f + expf(-z)); }
         if (lane == 0) a[(size_t)tj * ff + f] = from_f32<T>(z);
     }
 }
 
-// a [n, top, ff] (T), w_down [E, hidden, ff], idx, wt [n, top] -> y [n, hidden]
+// a [n, top, ff] (T), w_down [E, hidden, ff], idx [n, top] -> part [n, top, hidden]: every (token, choice) pair's
+// own result; gi_moe_combine sums a token's pairs with the router's weights.  A block stages one pair's vector.
 template <typename T>
 __global__ void __launch_bounds__(MOE_WARPS * 32)
 moe_down_kernel(const T* __restrict__ a, const T* __restrict__ w_down, const int* __restrict__ idx,
-                const float* __restrict__ wt, T* __restrict__ y, int top, int E, int ff, int hidden) {
+                T* __restrict__ part, int E, int ff, int hidden, int rows_pb) {
     gi_pdl_start();
-    extern __shared__ float as[];                   // top * ff
-    const int t = blockIdx.x;
+    extern __shared__ float as[];                   // ff
+    const int tj = blockIdx.x;
+    const int e = idx[tj];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int c = threadIdx.x; c < top * ff; c += blockDim.x) as[c] = to_f32(a[(size_t)t * top * ff + c]);
+    for (int c = threadIdx.x; c < ff; c += blockDim.x) as[c] = to_f32(a[(size_t)tj * ff + c]);
     __syncthreads();
-    for (int c = blockIdx.y * MOE_ROWS + warp; c < min(hidden, (int)(blockIdx.y + 1) * MOE_ROWS); c += MOE_WARPS) {
-        float acc = 0.f;
-        for (int j = 0; j < top; ++j) {
-            const int e = idx[(size_t)t * top + j];
-            if (e < 0 || e >= E) continue;
-            acc = fmaf(wt[(size_t)t * top + j], dot_row<T>(w_down + ((size_t)e * hidden + c) * ff, as + (size_t)j * ff, ff, lane), acc);
-        }
-        if (lane == 0) y[(size_t)t * hidden + c] = from_f32<T>(acc);
+    const bool ok = e >= 0 && e < E;
+    for (int c = blockIdx.y * rows_pb + warp; c < min(hidden, (int)(blockIdx.y + 1) * rows_pb); c += MOE_WARPS) {
+        const float z = ok ? dot_row<T>(w_down + ((size_t)e * hidden + c) * ff, as, ff, lane) : 0.f;
+        if (lane == 0) part[(size_t)tj * hidden + c] = from_f32<T>(z);
     }
 }
 
 extern "C" int gi_moe_up(const void* x, long long ldx, const void* w_up, const int* idx, void* a, int act_dtype, int n_rows,
                          int top, int E, int ff, int hidden, int act, void* stream) {
     GI_REQUIRE(n_rows >= 0 && top > 0 && E > 0 && ff > 0 && hidden > 0 && ldx >= hidden, "gi_moe_up: sizes");
-    GI_REQUIRE((ff + MOE_ROWS - 1) / MOE_ROWS <= 65535 && (act == 0 || act == 1), "gi_moe_up: %d rows per expert, activation %d", ff, act);
+    GI_REQUIRE((ff + MOE_WARPS - 1) / MOE_WARPS <= 65535 && (act == 0 || act == 1), "gi_moe_up: %d rows per expert, activation %d", ff, act);
     if (n_rows == 0) return 0;
     const size_t smem = (size_t)hidden * sizeof(float);
-    dim3 grid(n_rows * top, (ff + MOE_ROWS - 1) / MOE_ROWS);
+    const int rows_pb = moe_rows_per_block(n_rows * top, ff);
+    dim3 grid(n_rows * top, (ff + rows_pb - 1) / rows_pb);
     cudaStream_t s = (cudaStream_t)stream;
     if (act_dtype == GI_DTYPE_F32) {
         if (smem > 48 * 1024) { int rc = gi_reserve_smem((const void*)moe_up_kernel<float>, smem, "gi_moe_up"); if (rc) return rc; }
-        gi_launch(moe_up_kernel<float>, grid, dim3(MOE_WARPS * 32), smem, s, (const float*)x, ldx, (const float*)w_up, idx, (float*)a, top, E, ff, hidden, act);
+        gi_launch(moe_up_kernel<float>, grid, dim3(MOE_WARPS * 32), smem, s, (const float*)x, ldx, (const float*)w_up, idx, (float*)a, top, E, ff, hidden, act, rows_pb);
     } else if (act_dtype == GI_DTYPE_BF16) {
         if (smem > 48 * 1024) { int rc = gi_reserve_smem((const void*)moe_up_kernel<bf16>, smem, "gi_moe_up"); if (rc) return rc; }
-        gi_launch(moe_up_kernel<bf16>, grid, dim3(MOE_WARPS * 32), smem, s, (const bf16*)x, ldx, (const bf16*)w_up, idx, (bf16*)a, top, E, ff, hidden, act);
+        gi_launch(moe_up_kernel<bf16>, grid, dim3(MOE_WARPS * 32), smem, s, (const bf16*)x, ldx, (const bf16*)w_up, idx, (bf16*)a, top, E, ff, hidden, act, rows_pb);
     } else {
         GI_REQUIRE(false, "gi_moe_up: activation dtype %d", act_dtype);
     }
     return gi_check_launch("gi_moe_up");
 }
 
-extern "C" int gi_moe_down(const void* a, const void* w_down, const int* idx, const float* wt, void* y, int act_dtype,
+extern "C" int gi_moe_down(const void* a, const void* w_down, const int* idx, void* part, int act_dtype,
                            int n_rows, int top, int E, int ff, int hidden, void* stream) {
     GI_REQUIRE(n_rows >= 0 && top > 0 && E > 0 && ff > 0 && hidden > 0, "gi_moe_down: sizes");
-    GI_REQUIRE((hidden + MOE_ROWS - 1) / MOE_ROWS <= 65535, "gi_moe_down: %d output channels", hidden);
+    GI_REQUIRE((hidden + MOE_WARPS - 1) / MOE_WARPS <= 65535, "gi_moe_down: %d output channels", hidden);
     if (n_rows == 0) return 0;
-    const size_t smem = (size_t)top * ff * sizeof(float);
-    GI_REQUIRE(smem <= 200 * 1024, "gi_moe_down: %d chosen experts of %d do not fit shared memory", top, ff);
-    dim3 grid(n_rows, (hidden + MOE_ROWS - 1) / MOE_ROWS);
+    const size_t smem = (size_t)ff * sizeof(float);
+    GI_REQUIRE(smem <= 200 * 1024, "gi_moe_down: an expert of %d does not fit shared memory", ff);
+    const int rows_pb = moe_rows_per_block(n_rows * top, hidden);
+    dim3 grid(n_rows * top, (hidden + rows_pb - 1) / rows_pb);
     cudaStream_t s = (cudaStream_t)stream;
     if (act_dtype == GI_DTYPE_F32) {
         if (smem > 48 * 1024) { int rc = gi_reserve_smem((const void*)moe_down_kernel<float>, smem, "gi_moe_down"); if (rc) return rc; }
-        gi_launch(moe_down_kernel<float>, grid, dim3(MOE_WARPS * 32), smem, s, (const float*)a, (const float*)w_down, idx, wt, (float*)y, top, E, ff, hidden);
+        gi_launch(moe_down_kernel<float>, grid, dim3(MOE_WARPS * 32), smem, s, (const float*)a, (const float*)w_down, idx, (float*)part, E, ff, hidden, rows_pb);
     } else if (act_dtype == GI_DTYPE_BF16) {
         if (smem > 48 * 1024) { int rc = gi_reserve_smem((const void*)moe_down_kernel<bf16>, smem, "gi_moe_down"); if (rc) return rc; }
-        gi_launch(moe_down_kernel<bf16>, grid, dim3(MOE_WARPS * 32), smem, s, (const bf16*)a, (const bf16*)w_down, idx, wt, (bf16*)y, top, E, ff, hidden);
+        gi_launch(moe_down_kernel<bf16>, grid, dim3(MOE_WARPS * 32), smem, s, (const bf16*)a, (const bf16*)w_down, idx, (bf16*)part, E, ff, hidden, rows_pb);
     } else {
         GI_REQUIRE(false, "gi_moe_down: activation dtype %d", act_dtype);
     }
@@ -208,7 +254,7 @@ __global__ void moe_combine_kernel(const T* __restrict__ buf, const int* __restr
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < hidden; c += gridDim.y * blockDim.x) {
         float acc = 0.f;
         for (int j = 0; j < top; ++j)
-            acc = fmaf(wt[t * top + j], to_f32(buf[(size_t)where[t * top + j] * hidden + c]), acc);
+            acc = fmaf(wt[t * top + j], to_f32(buf[(size_t)(where ? where[t * top + j] : (int)(t * top + j)) * hidden + c]), acc);
         y[t * hidden + c] = from_f32<T>(acc);
     }
 }

@@ -281,6 +281,8 @@ def attn_finish(att: torch.Tensor, heads: int, maps: int, lam: Optional[torch.Te
     if out is None:
         out = torch.empty((n, heads * dv), dtype=act_dtype, device=att.device)
     _rows(out, "out", act_dtype)
+    if out.shape != (n, heads * dv):
+        raise KernelError(f"out {tuple(out.shape)} for a result of {(n, heads * dv)}")
     check(l.gi_attn_finish(_ptr(att), code(att.dtype), maps, _ptr(lam), float(norm_eps or 0.0), int(norm_eps is not None),
                            float(mul), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(out), out.stride(0),
                            code(act_dtype), n, heads, dv, _stream()), l)
@@ -358,6 +360,18 @@ def scaled_sum(a: torch.Tensor, ca: float, b: torch.Tensor, cb: float) -> torch.
     return out
 
 
+def router_logits(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """x [n, hidden] . w[experts, hidden]^T as float32, for a float32 weight and activations of either type."""
+    l = require_gpu()
+    _rows(x, "x"), _dense(w, "w", torch.float32)
+    n, hidden = x.shape
+    if w.shape[1] != hidden:
+        raise KernelError(f"router weight {tuple(w.shape)} for rows of {hidden}")
+    z = torch.empty((n, w.shape[0]), dtype=torch.float32, device=x.device)
+    check(l.gi_router_logits(_ptr(x), x.stride(0), code(x.dtype), _ptr(w), _ptr(z), n, w.shape[0], hidden, _stream()), l)
+    return z
+
+
 def router_topk(logits: torch.Tensor, top: int):
     """(chosen experts int32 [n, top] in falling order of their logits, softmax over the chosen logits float32)."""
     l = require_gpu()
@@ -380,19 +394,20 @@ def moe_rowwise(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, idx: 
     E, ff, _ = w_up.shape
     top = idx.shape[1]
     a = torch.empty((n, top, ff), dtype=x.dtype, device=x.device)
-    y = torch.empty((n, hidden), dtype=x.dtype, device=x.device)
+    part = torch.empty((n * top, hidden), dtype=x.dtype, device=x.device)
     act = {"relu_squared": 0, "silu": 1}[activation]
     check(l.gi_moe_up(_ptr(x), x.stride(0), _ptr(w_up), _ptr(idx), _ptr(a), code(x.dtype), n, top, E, ff, hidden, act,
                       _stream()), l)
-    check(l.gi_moe_down(_ptr(a), _ptr(w_down), _ptr(idx), _ptr(wt), _ptr(y), code(x.dtype), n, top, E, ff, hidden,
-                        _stream()), l)
-    return y
+    check(l.gi_moe_down(_ptr(a), _ptr(w_down), _ptr(idx), _ptr(part), code(x.dtype), n, top, E, ff, hidden, _stream()), l)
+    return moe_combine(part, None, wt)
 
 
-def moe_combine(buf: torch.Tensor, where: torch.Tensor, wt: torch.Tensor) -> torch.Tensor:
-    """y[t] = sum_j wt[t, j] buf[where[t, j]] (float32 sums in the order of j)."""
+def moe_combine(buf: torch.Tensor, where: Optional[torch.Tensor], wt: torch.Tensor) -> torch.Tensor:
+    """y[t] = sum_j wt[t, j] buf[where[t, j]] (float32 sums in the order of j); without `where`: row t * top + j."""
     l = require_gpu()
-    _dense(buf, "buf"), _dense(where, "where", torch.int32), _dense(wt, "wt", torch.float32)
+    _dense(buf, "buf"), _dense(wt, "wt", torch.float32)
+    if where is not None:
+        _dense(where, "where", torch.int32)
     n, top = wt.shape
     y = torch.empty((n, buf.shape[1]), dtype=buf.dtype, device=buf.device)
     check(l.gi_moe_combine(_ptr(buf), _ptr(where), _ptr(wt), _ptr(y), code(buf.dtype), n, top, buf.shape[1], _stream()), l)
@@ -442,18 +457,23 @@ def xielu(z: torch.Tensor, pq: torch.Tensor) -> torch.Tensor:
 
 
 def gated_group_rmsnorm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, groups: int,
-                        gate_kind: str) -> torch.Tensor:
+                        gate_kind: str, mul: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """o float32 [n, groups * gs]: each group divided by its root mean square, times weight (one per column, or
-    one per column of a group), times sigmoid(gate) or silu(gate); returns gate's type."""
+    one per column of a group), times sigmoid(gate) or silu(gate), times `mul`; returns gate's type.  `out` may be
+    columns of a wider matrix."""
     l = require_gpu()
     _dense(o, "o", torch.float32), _rows(gate, "gate"), _dense(weight, "weight")
     n, cols = o.shape
     if cols % groups or gate.shape != (n, cols):
         raise KernelError(f"o {tuple(o.shape)} in {groups} groups, gate {tuple(gate.shape)}")
-    out = torch.empty((n, cols), dtype=gate.dtype, device=o.device)
+    if out is None:
+        out = torch.empty((n, cols), dtype=gate.dtype, device=o.device)
+    _rows(out, "out", gate.dtype)
+    if out.shape != (n, cols):
+        raise KernelError(f"out {tuple(out.shape)} for a result of {(n, cols)}")
     check(l.gi_gated_group_rmsnorm(_ptr(o), _ptr(gate), gate.stride(0), _ptr(weight), code(weight.dtype), weight.numel(),
                                    _ptr(out), code(gate.dtype), n, groups, cols // groups, float(eps),
-                                   {"sigmoid": 0, "silu": 1}[gate_kind], _stream()), l)
+                                   {"sigmoid": 0, "silu": 1}[gate_kind], float(mul), out.stride(0), _stream()), l)
     return out
 
 
@@ -921,10 +941,12 @@ def tcgen05_attention_takes(dtype: torch.dtype, head_dim: int, page_size: int) -
 
 
 def attention_prefill_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
-                              q_tiles128: torch.Tensor, scale: float, window: int, rows_covered: bool = False) -> torch.Tensor:
+                              q_tiles128: torch.Tensor, scale: float, window: int, rows_covered: bool = False,
+                              chunk: int = 0) -> torch.Tensor:
     """Flash attention of q [n, n_q, 128] over the paged cache on tcgen05 tensor cores (TMA-fed, S, P and
     P V in tensor memory).  `q_tiles128` int32 [n_tiles, 4] cuts the rows into runs of at most 128
-    consecutive tokens of one sequence: {slot, first row, rows, position of the first row}."""
+    consecutive tokens of one sequence: {slot, first row, rows, position of the first row}.  `chunk` > 0: a query
+    sees only the keys of its own chunk of positions."""
     l = require_gpu()
     _dense(q, "q", torch.bfloat16), _dense(k_pool, "k_pool", torch.bfloat16), _dense(v_pool, "v_pool", torch.bfloat16)
     _dense(block_table, "block_table", torch.int32), _dense(q_tiles128, "q_tiles128", torch.int32)
@@ -938,7 +960,7 @@ def attention_prefill_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: tor
     out = (torch.empty if rows_covered else torch.zeros)((n, n_q * d), dtype=q.dtype, device=q.device)
     check(l.gi_attention_prefill_tcgen05(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), _ptr(q_tiles128),
                                          q_tiles128.shape[0], _ptr(out), n, n_q, n_kv, d, page_size,
-                                         block_table.shape[1], n_pages, int(window or 0), float(scale),
+                                         block_table.shape[1], n_pages, int(window or 0), int(chunk or 0), float(scale),
                                          _ptr(tcgen05_error_flag(q.device)), _stream()), l)
     return out
 

@@ -40,14 +40,15 @@ _SIGNATURES = {
     "gi_glu": ([P, L, P, I, I, I, I, P], I),
     "gi_relu_squared": ([P, P, I, L, P], I),
     "gi_scaled_sum": ([P, F, P, F, P, I, L, P], I),
+    "gi_router_logits": ([P, L, I, P, P, I, I, I, P], I),
     "gi_router_topk": ([P, L, I, I, P, P, I, P], I),
     "gi_moe_up": ([P, L, P, P, P, I, I, I, I, I, I, I, P], I),
-    "gi_moe_down": ([P, P, P, P, P, I, I, I, I, I, I, P], I),
+    "gi_moe_down": ([P, P, P, P, I, I, I, I, I, I, P], I),
     "gi_moe_combine": ([P, P, P, P, I, I, I, I, P], I),
     "gi_causal_conv": ([P, L, I, I, P, I, I, P, L, P, P, I, I, I, P], I),
     "gi_gate_norm_add": ([P, L, P, L, P, I, P, I, P, P, I, I, I, F, P], I),
     "gi_xielu": ([P, L, P, I, P, I, I, I, P], I),
-    "gi_gated_group_rmsnorm": ([P, P, L, P, I, I, P, I, I, I, I, F, I, P], I),
+    "gi_gated_group_rmsnorm": ([P, P, L, P, I, I, P, I, I, I, I, F, I, F, L, P], I),
     "gi_causal_conv_silu": ([P, L, I, I, P, I, I, P, L, P, P, I, I, P], I),
     "gi_scan_state_floats": ([I, I], L),
     "gi_decay_scan": ([P, L, I, I, I, I, P, P, L, P, P, P, I, I, I, I, P], I),
@@ -59,7 +60,7 @@ _SIGNATURES = {
     "gi_attention_prefill_masked_bf16": ([P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, I, I, F, P], I),
     "gi_attention_decode_masked_bf16": ([P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, I, P], I),
     "gi_attention_mma_takes": ([I, I], I),
-    "gi_attention_prefill_tcgen05": ([P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, F, P, P], I),
+    "gi_attention_prefill_tcgen05": ([P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, I, F, P, P], I),
     "gi_attention_decode_bf16": ([P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P], I),
     "gi_set_pdl": ([I], None),
     "gi_attention_decode_tcgen05": ([P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P], I),

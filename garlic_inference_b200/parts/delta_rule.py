@@ -97,8 +97,9 @@ class GatedDeltaRule(Mixer):
     def step_arrays(self, shape, cache):
         return {} if shape.all_single else {"seq_spans": lambda: seq_spans_array(shape)}
 
-    def pre_output(self, x, ctx, cache, position, writes_cache=True):
-        """Everything before the output projection: [n, n_heads * value_dim] in the activation type."""
+    def pre_output(self, x, ctx, cache, position, writes_cache=True, out=None, out_mul=1.0):
+        """Everything before the output projection: [n, n_heads * value_dim] in the activation type, times
+        `out_mul`, written into `out` (columns of a wider matrix) when given."""
         if not writes_cache:
             raise ValueError("a mixer with state of its own cannot read another layer's")
         proj = linear(x, self.w_in)
@@ -118,7 +119,8 @@ class GatedDeltaRule(Mixer):
             gate = linear(proj[:, self.g_off:self.g_off + self.gate_rank].contiguous(), self.w_g2)
         else:
             gate = proj[:, self.g_off:self.g_off + self.H * self.dv]
-        return kernels.gated_group_rmsnorm(o, gate, self.norm, self.eps, groups=self.H, gate_kind=self.out_gate)
+        return kernels.gated_group_rmsnorm(o, gate, self.norm, self.eps, groups=self.H, gate_kind=self.out_gate,
+                                           mul=out_mul, out=out)
 
     def step(self, x, ctx, cache, position, writes_cache=True):
         return linear(self.pre_output(x, ctx, cache, position, writes_cache), self.w_o)

@@ -19,7 +19,8 @@ value tensors: the schedule points it at another layer's cache entry, whose keys
 them: after convolution and rotation) it reads with its own queries, mask and everything else.
 
 All projections that read x are one packed product.  Which attention runs: in bfloat16, with key and value
-sizes that the tensor-core kernels take (multiples of 16 up to 128, equal or one twice the other): the flash
+sizes that the tensor-core kernels take (multiples of 16 up to 128, equal or one twice the other; one map with
+keys and values of 128 and pages of a multiple of 64 tokens: the tcgen05 prompt kernel): the flash
 kernel for steps that bring several tokens of a sequence and the split-KV kernel for decode steps, once per map,
 with the chunk mask in them (float32 scores, softmax and sums; the weights rounded to bfloat16 as the second
 product's operand).  Everything else (float32, other sizes): the exact-order kernel, whose result at a position does not depend on how the tokens were cut into steps.  What
@@ -113,10 +114,16 @@ class MaskedAttention(Mixer):
     def _tensor_cores(self) -> bool:
         return kernels.mma_attention_takes(self.rt.dtype, self.d, self.dv)
 
+    def _run_rows(self, kv) -> int:
+        """Height of the query runs of the prompt kernel that takes this mixer: 128 (tcgen05: one map, keys and
+        values of 128, pages of a multiple of 64), 64 (mma.sync), 0 (the exact-order kernel, which needs none)."""
+        if self.maps == 1 and self.d == self.dv and kernels.tcgen05_attention_takes(self.rt.dtype, self.d, kv.page_size):
+            return 128
+        return 64 if self._tensor_cores() else 0
+
     def step_arrays(self, shape, cache):
-        if shape.all_single or not self._tensor_cores():
-            return {}
-        return {"query_runs_64": lambda: query_runs(shape, 64)}
+        rows = 0 if shape.all_single else self._run_rows(cache.kv)
+        return {f"query_runs_{rows}": lambda: query_runs(shape, rows)} if rows else {}
 
     def _rotation(self, position):
         if position is None:
@@ -132,8 +139,9 @@ class MaskedAttention(Mixer):
     def step(self, x, ctx, cache, position, writes_cache=True):
         return linear(self.pre_output(x, ctx, cache, position, writes_cache), self.w_o)
 
-    def pre_output(self, x, ctx, cache, position, writes_cache=True):
-        """Everything before the output projection: [n, n_heads * value_dim] in the activation type."""
+    def pre_output(self, x, ctx, cache, position, writes_cache=True, out=None, out_mul=1.0):
+        """Everything before the output projection: [n, n_heads * value_dim] in the activation type, times
+        `out_mul`, written into `out` (columns of a wider matrix) when given."""
         kv = cache.kv
         if self.own_kv != bool(writes_cache):
             raise ValueError("a layer with keys and values of its own writes its cache entry, and one without reads "
@@ -156,19 +164,26 @@ class MaskedAttention(Mixer):
         if ctx.all_single and self._tensor_cores() and self.H // self.G <= 16:
             att = kernels.attention_decode_masked_bf16(q, kv.k_pool, kv.v_pool, kv.block_table, ctx.tok_pos, ctx.tok_slot,
                                                        self.scale, window=self.window, chunk=self.chunk, maps=self.maps)
-        elif not ctx.all_single and ctx.seq_lens and self._tensor_cores():
-            runs = ctx.arrays.get("query_runs_64")
+        elif not ctx.all_single and ctx.seq_lens and self._run_rows(kv):
+            rows = self._run_rows(kv)
+            runs = ctx.arrays.get(f"query_runs_{rows}")
             if runs is None:                      # a context put together by hand: cut and copy here
-                runs = ctx.arrays["query_runs_64"] = torch.from_numpy(query_runs(ctx, 64)).to(x.device)
-            att = kernels.attention_prefill_masked_bf16(q, kv.k_pool, kv.v_pool, kv.block_table, runs, self.scale,
-                                                        window=self.window, chunk=self.chunk, maps=self.maps,
-                                                        rows_covered=ctx.n_tokens == sum(ctx.seq_lens))
+                runs = ctx.arrays[f"query_runs_{rows}"] = torch.from_numpy(query_runs(ctx, rows)).to(x.device)
+            covered = ctx.n_tokens == sum(ctx.seq_lens)
+            if rows == 128:
+                att = kernels.attention_prefill_tcgen05(q, kv.k_pool, kv.v_pool, kv.block_table, runs, self.scale,
+                                                        self.window, rows_covered=covered, chunk=self.chunk)
+            else:
+                att = kernels.attention_prefill_masked_bf16(q, kv.k_pool, kv.v_pool, kv.block_table, runs, self.scale,
+                                                            window=self.window, chunk=self.chunk, maps=self.maps,
+                                                            rows_covered=covered)
         else:
             att = kernels.attention_masked(q, kv.k_pool, kv.v_pool, kv.block_table, ctx.tok_pos, ctx.tok_slot,
                                            self.scale, ctx.status, window=self.window, chunk=self.chunk,
                                            maps=self.maps, out_float32=True)
         gate = proj[:, self.g_off:self.g_off + self.H] if self.head_gate else None
-        return kernels.attn_finish(att, self.H, self.maps, self.lam, self.sub_norm_eps, self.out_mul, gate, self.rt.dtype)
+        return kernels.attn_finish(att, self.H, self.maps, self.lam, self.sub_norm_eps, self.out_mul * out_mul, gate,
+                                   self.rt.dtype, out=out)
 
 
 register_part(MaskedAttention.kind, MaskedAttention)

@@ -1,16 +1,19 @@
 """A routed feed-forward (mixture of experts), as a feed-forward part.
 
-    z = Wr x                                   router logits, float32 (the weight is widened, the product is this
-                                               package's float32 kernel; x may be its 16-bit rounding)
+    z = Wr x                                   router logits, float32 (the weight is widened, the product is a
+                                               float32 kernel of its own; x may be its 16-bit rounding)
     the `top` experts with the largest z are chosen; their weights are the softmax over the chosen z alone
     y = sum_e weight_e Wd_e act(Wu_e x)        act: the square of relu ("relu_squared") or silu; no biases
 
 The experts' matrices are stacked at load time ([experts, ff, hidden] and [experts, hidden, ff]).  Two ways to
 run them.  A step of a few rows (a decode step; such a step may be recorded, so nothing may come back to the
-host): two kernels that read the chosen experts' matrices only, a warp per matrix row, the experts taken from
-device memory.  More rows: the (token, choice) pairs are sorted by expert on the device, the counts come to the
-host once, every expert that was chosen runs two matrix products over its own rows, and one kernel sums each
-token's `top` results with its weights in the router's order.  Either way a token's result does not depend on
+host): kernels that read the chosen experts' matrices only, a warp per matrix row, the experts taken from
+device memory.  More rows: the (token, choice) pairs are sorted by expert on the device, the experts run two
+matrix products over their own rows, and one kernel sums each token's `top` results with its weights in the
+router's order.  In bfloat16 the two products are the library's grouped product (`torch._grouped_mm`: the rows
+of every expert in one launch, the groups' ends read from device memory, nothing comes to the host); in float32,
+or where the library has no grouped product, the counts come to the host once and every chosen expert runs this
+package's products over its rows.  Either way a token's result does not depend on
 the other tokens of the step beyond the rounding of the products.
 NikolayBlagoev/garlic-inference's mixture-of-experts model is a different design (src/models/qwen3/qwen3-moe.cpp).
 """
@@ -23,7 +26,9 @@ from ..weights.loader import TensorWant
 from .base import FeedForward, register_part
 
 # Up to how many rows of a step the row-by-row kernels run (beyond: expert by expert through matrix products).
-ROWWISE_MAX_ROWS = 32
+# The row-by-row kernels read an expert's matrices once per (token, choice) pair, the grouped product once per
+# expert: from a few tokens on, pairs share experts.
+ROWWISE_MAX_ROWS = 8
 
 
 class RoutedExperts(FeedForward):
@@ -48,6 +53,7 @@ class RoutedExperts(FeedForward):
         if self.activation not in ("relu_squared", "silu"):
             raise ValueError(f"expert activation {self.activation!r} is neither 'relu_squared' nor 'silu'")
         self.w_router = load("router").to(torch.float32)
+        self._next_expert = torch.arange(1, self.E + 1, dtype=torch.int64, device=rt.device)
         names = [f"e{e}.up" for e in range(self.E)]
         dtype = load.dtype(*names, *(f"e{e}.down" for e in range(self.E)))
         self.w_up = torch.empty((self.E, self.ff, self.hidden), dtype=dtype, device=rt.device)
@@ -58,25 +64,38 @@ class RoutedExperts(FeedForward):
 
     def step(self, x, ctx):
         n = x.shape[0]
-        logits = linear(x, self.w_router, out_dtype=torch.float32)
+        logits = kernels.router_logits(x, self.w_router)
         idx, wt = kernels.router_topk(logits, self.top)
-        if ctx.captured or n <= ROWWISE_MAX_ROWS or self.activation != "relu_squared":
+        grouped = self._grouped(x)
+        if n <= ROWWISE_MAX_ROWS or self.activation != "relu_squared" or (ctx.captured and not grouped):
             return kernels.moe_rowwise(x, self.w_up, self.w_down, idx, wt, self.activation)
         # expert by expert: pairs (token, choice) sorted by expert; `where` is each pair's row in that order
         flat = idx.reshape(-1)
-        order = torch.sort(flat.to(torch.int64), stable=True).indices
+        experts, order = torch.sort(flat.to(torch.int64), stable=True)
         where = torch.empty_like(order)
         where[order] = torch.arange(order.numel(), device=order.device)
-        counts = torch.bincount(flat, minlength=self.E).tolist()           # the one trip to the host
+        # where each expert's rows end in the sorted order: the pairs whose expert is below e + 1
+        ends = torch.searchsorted(experts, self._next_expert).to(torch.int32)
         rows = x.index_select(0, order // self.top)
-        buf = torch.empty((n * self.top, self.hidden), dtype=x.dtype, device=x.device)
-        at = 0
-        for e, c in enumerate(counts):
-            if c:
-                a = kernels.relu_squared(linear(rows[at:at + c], self.w_up[e]))
-                buf[at:at + c] = linear(a, self.w_down[e])
-                at += c
-        return kernels.moe_combine(buf, where.to(torch.int32).view(n, self.top), wt)
+        if grouped:
+            a = kernels.relu_squared(torch._grouped_mm(rows, self.w_up.transpose(1, 2), offs=ends))
+            buf = torch._grouped_mm(a, self.w_down.transpose(1, 2), offs=ends)
+        else:
+            buf = torch.empty((n * self.top, self.hidden), dtype=x.dtype, device=x.device)
+            at = 0
+            bounds = [0] + ends.tolist()                                   # the one trip to the host
+            for e in range(self.E):
+                c = bounds[e + 1] - bounds[e]
+                if c:
+                    a = kernels.relu_squared(linear(rows[at:at + c], self.w_up[e]))
+                    buf[at:at + c] = linear(a, self.w_down[e])
+                    at += c
+        return kernels.moe_combine(buf.contiguous(), where.to(torch.int32).view(n, self.top), wt)
+
+    def _grouped(self, x) -> bool:
+        """Whether the library's grouped product takes these operands: bfloat16, rows of 16-byte multiples."""
+        return (x.dtype == torch.bfloat16 and self.w_up.dtype == torch.bfloat16 and hasattr(torch, "_grouped_mm")
+                and self.hidden % 8 == 0 and self.ff % 8 == 0)
 
 
 register_part(RoutedExperts.kind, RoutedExperts)

@@ -6,12 +6,21 @@
 tensors are this part's tensors under "left." and "right.".  The cache entry of the layer holds what both need:
 the paged keys and values of the one and the per-sequence state of the other (two sides that both want pages, or
 both want state, are refused).  The position encoding of the layer goes to both sides; a side that rotates
-nothing ignores it.  Upstream has no such layer.
+nothing ignores it.
+
+When both sides end in an output projection of their own and can hand over what goes into it (`pre_output`,
+`w_o`), the two projections and the weighted sum are one product: each side writes its activations, times its
+factor, into its columns of one matrix, and the two output weights lie side by side,
+    y = [ left_scale a_left | right_scale a_right ] . [ Wo_left | Wo_right ]^T,
+summed in float32 inside the product.  Otherwise the sides run whole and a kernel adds their results.
+Upstream has no such layer.
 """
 from __future__ import annotations
 
 from ..cache import EntryRequirement, split_requirement
-from ..ops import kernels
+import torch
+
+from ..ops import kernels, linear
 from .base import Mixer, part_class, register_part
 
 
@@ -45,6 +54,14 @@ class ParallelMixers(Mixer):
         make = lambda side: part_class(params[side]["kind"])(params[side]["params"], _SideLoader(load, side + "."), rt)
         self.left, self.right = make("left"), make("right")
         self.left_scale, self.right_scale = float(params.get("left_scale", 1.0)), float(params.get("right_scale", 1.0))
+        self.w_o = None
+        sides = (self.left, self.right)
+        if all(hasattr(m, "pre_output") and getattr(m, "w_o", None) is not None for m in sides) and \
+                self.left.w_o.dtype == self.right.w_o.dtype and self.left.w_o.shape[1] % 8 == 0:
+            self.k_left = self.left.w_o.shape[1]
+            self.w_o = torch.cat([self.left.w_o, self.right.w_o], dim=1).contiguous()
+            self.left.w_o = self.w_o[:, :self.k_left]            # views: the sides' own copies are let go
+            self.right.w_o = self.w_o[:, self.k_left:]
 
     @property
     def graph_safe(self):
@@ -63,6 +80,11 @@ class ParallelMixers(Mixer):
         return {**self.left.step_arrays(shape, cache), **self.right.step_arrays(shape, cache)}
 
     def step(self, x, ctx, cache, position, writes_cache=True):
+        if self.w_o is not None:
+            acts = torch.empty((x.shape[0], self.w_o.shape[1]), dtype=self.rt.dtype, device=x.device)
+            self.left.pre_output(x, ctx, cache, position, writes_cache, out=acts[:, :self.k_left], out_mul=self.left_scale)
+            self.right.pre_output(x, ctx, cache, position, writes_cache, out=acts[:, self.k_left:], out_mul=self.right_scale)
+            return linear(acts, self.w_o)
         a = self.left.step(x, ctx, cache, position, writes_cache)
         b = self.right.step(x, ctx, cache, position, writes_cache)
         return kernels.scaled_sum(a, self.left_scale, b, self.right_scale)

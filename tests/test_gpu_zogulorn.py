@@ -140,6 +140,25 @@ def test_keys_at_chunk_edges_and_page_borders(name, chunk, dtype, folder, tmp_pa
                     assert errs[("n", p)][1] <= shows[p] / 3, f"position {p}"
 
 
+def test_heads_of_128_on_pages_of_64_run_the_tcgen05_prompt_kernel(model, folder):
+    """bfloat16, heads of 128, pages of 64 tokens: prompts and portions go through the tcgen05 kernel with the chunk
+    mask in it (chunks of 70: edges inside its tiles of 64 keys and 128 queries), decode steps through the split-KV
+    kernel; all against the plain model."""
+    from garlic_inference_b200.ops import counters
+    m = model("wide", "bfloat16", max_tokens=2048, page_size=64, max_slots=4)
+    reqs = _requests("wide", [300, 1, 141, 70], seed=15)
+    want, own = tz.plain_pair(folder("wide"), reqs)
+    for what, steps in (("whole", tiny.trace_whole(reqs)), ("tail", tiny.trace_tail_by_one(reqs, tail=80)),
+                        ("portions", tz.trace_portions(reqs, [129, 3, 64], together=True))):
+        got = tiny.run_trace_in_process(m, steps)
+        tiny.assert_covers(got, reqs)
+        tz.judge(got, want, own, "bfloat16", f"wide {what}")
+    mixer = m.model.blocks[0].mixer.left
+    assert mixer._run_rows(m.engine.cache.view(0).kv) == 128
+    from garlic_inference_b200.ops import kernels
+    kernels.check_bounded_waits(torch.device("cuda", 0))
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["mix", "right", "moe"])
 def test_long_decoding(name, dtype, model, folder):
@@ -289,7 +308,7 @@ def test_routed_experts_few_rows_and_many_rows_agree(folder):
     x = torch.randn(70, 48, device="cuda")
     z = torch.zeros(70, dtype=torch.int32, device="cuda")
     many = part.step(x, StepContext(70, z, z, z))
-    few = torch.cat([part.step(x[i:i + 10].contiguous(), StepContext(10, z, z, z)) for i in range(0, 70, 10)])
+    few = torch.cat([part.step(x[i:i + 7].contiguous(), StepContext(7, z, z, z)) for i in range(0, 70, 7)])
     torch.testing.assert_close(many, few, rtol=1e-5, atol=1e-6)
     w = {n[len("l0.mlp."):]: ck.tensor(n).float() for n in ck.names() if n.startswith("l0.mlp.")}
     torch.testing.assert_close(many.cpu(), plain.moe_ff(x.cpu(), w, {"router": {"experts": 5, "top": 2}}), rtol=1e-4, atol=1e-5)

@@ -68,6 +68,11 @@ TINY = {
                         _with(_attention(4, 2, 16, 24, 17, 2, diff=0.6, kv_from=0), _dense(64)),
                         _with(_parallel(_left(2, 2, 32, 32, 25), _right(4, 1, 16, 36, 3)), _moe(32, 4, 4)),
                         _with(_attention(4, 2, 16, 24, 50, 3, diff=0.2, kv_from=0))]),
+    # heads of 128 (the prompt kernel on tcgen05 when the cache's pages are multiples of 64 tokens), chunks that are
+    # no multiple of its tiles
+    "wide": dict(vocab=300, width=64, eps=1e-5, emb=2.0, seed=28, std=0.08, norm_std=0.1,
+                 layers=[_with(_parallel(_left(2, 1, 128, 128, 70, dims=64, scale=1.0), _right(2, 1, 8, 8, 2), a=1.1, b=0.4),
+                               _dense(64))]),
     # one head, one key head, one tap (no filter state), chunks of one position, one expert of one, rotation of
     # the whole head and of none of it
     "ones": dict(vocab=257, width=48, eps=1e-5, emb=1.5, seed=27, std=0.1, norm_std=0.2,
