@@ -70,9 +70,11 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // and head h / group).  That is what a mixer with several softmax maps per head over the same values needs: map
 // m of a head lies at q_o = m D, reads key head kvh * maps + m, and writes beside the other maps.  chunk > 0: a
 // query sees only the keys of its own chunk of positions (chunks counted from position 0).
+// maps > 1: one launch serves all maps; the grid's head axis is then maps times as long and block y belongs to map
+// y / heads, which adds map * D to q_o, map to k_add and map * DV to o_o.
 struct AttnLayout {
     long long q_ts, q_hs, q_o, o_ts, o_hs, o_o;
-    int n_kh, k_mul, k_add, chunk;
+    int n_kh, k_mul, k_add, chunk, maps;
 };
 
 // Element offset of row j of a sequence inside a pool (for key/value head kvh), or -1 when j is not below
@@ -233,7 +235,8 @@ flash_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool
 
     const int4 ti = tiles[blockIdx.x];
     const int slot = ti.x, row0 = ti.y, n_rows = ti.z, pos0 = ti.w;
-    const int h = blockIdx.y, kvh = h / (n_q / n_kv);
+    const int h = blockIdx.y % n_q, map = blockIdx.y / n_q, kvh = h / (n_q / n_kv);
+    lay.q_o += (long long)map * D; lay.o_o += (long long)map * DV; lay.k_add += map;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     if (slot < 0 || n_rows <= 0) return;
     const int* bt_row = block_table + (size_t)slot * max_pages;
@@ -341,8 +344,10 @@ decode_splitkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_poo
     bf16* sQ = reinterpret_cast<bf16*>(at_smem);                // 16 rows
     bf16* sKV = sQ + 16 * LD;                                    // [4 warps][AT_DEC_DEPTH][keys | values][16][LD]
 
-    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
-    const int grp = n_q / n_kv;
+    const int split = blockIdx.x, kvh = blockIdx.y % n_kv, map = blockIdx.y / n_kv, b = blockIdx.z;
+    const int grp = n_q / n_kv, maps = lay.maps > 1 ? lay.maps : 1;
+    lay.q_o += (long long)map * D; lay.k_add += map;
+    const size_t prow = ((size_t)b * maps + map) * n_q + (size_t)kvh * grp;      // first row of this block's partials
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int slot = tok_slot[b], pos = tok_pos[b];
     const int kv_len = pos + 1;
@@ -353,7 +358,7 @@ decode_splitkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_poo
     const int nt_all = slot < 0 ? 0 : (kv_len - lo_al + AT_BN - 1) / AT_BN;
     const int per = (nt_all + n_splits - 1) / n_splits;
     const int t0 = split * per, t1 = min(nt_all, t0 + per);
-    float* my_ml = part_ml + (((size_t)b * n_q + kvh * grp) * n_splits + split) * 2;
+    float* my_ml = part_ml + (prow * n_splits + split) * 2;
     gi_pdl_wait();                               // positions and slots above are set before the step's first kernel
     if (t0 >= t1) {                                              // nothing for this slice: an empty partial
         if (threadIdx.x < grp) {
@@ -477,7 +482,7 @@ decode_splitkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_poo
                 L += f * mL[w * 16 + r];
             }
         }
-        part_o[(((size_t)b * n_q + kvh * grp + r) * n_splits + split) * DV + dim] = acc;
+        part_o[((prow + r) * n_splits + split) * DV + dim] = acc;
         if (dim == 0) {
             my_ml[(size_t)r * n_splits * 2] = M;
             my_ml[(size_t)r * n_splits * 2 + 1] = L;
@@ -488,11 +493,12 @@ decode_splitkv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_poo
 template <int D>
 __global__ void __launch_bounds__(128)
 decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out,
-                      int n_splits, int n_q, long long o_ts, long long o_hs, long long o_o) {
+                      int n_splits, int n_q, long long o_ts, long long o_hs, long long o_o, int maps) {
     gi_pdl_start();
-    const size_t row = blockIdx.x;                               // sequence * n_q + head
-    // where the row's result goes: dense rows, or (n_q > 0) sequence * o_ts + head * o_hs + o_o
-    bf16* dst = n_q > 0 ? out + (row / n_q) * o_ts + (row % n_q) * o_hs + o_o : out + row * D;
+    const size_t row = blockIdx.x;                               // (sequence * maps + map) * n_q + head
+    // where the row's result goes: dense rows, or (n_q > 0) sequence * o_ts + head * o_hs + o_o + map * D
+    bf16* dst = n_q > 0 ? out + (row / ((size_t)n_q * maps)) * o_ts + (row % n_q) * o_hs + o_o + ((row / n_q) % maps) * D
+                        : out + row * D;
     const float* ml = part_ml + row * n_splits * 2;
     float M = -INFINITY;
     for (int s = 0; s < n_splits; ++s) M = fmaxf(M, ml[2 * s]);
@@ -571,16 +577,16 @@ static AttnLayout plain_layout(int n_q, int d, int dv) {
     AttnLayout lay;
     lay.q_ts = (long long)n_q * d; lay.q_hs = d; lay.q_o = 0;
     lay.o_ts = (long long)n_q * dv; lay.o_hs = dv; lay.o_o = 0;
-    lay.n_kh = 0; lay.k_mul = 1; lay.k_add = 0; lay.chunk = 0;
+    lay.n_kh = 0; lay.k_mul = 1; lay.k_add = 0; lay.chunk = 0; lay.maps = 1;
     return lay;
 }
 
-// Map m of `maps` per head: q [rows, n_q, maps, d], out [rows, n_q, maps, dv], key pool [pages, n_kv * maps, page, d].
-static AttnLayout map_layout(int n_q, int n_kv, int d, int dv, int maps, int m, int chunk) {
+// `maps` maps per head: q [rows, n_q, maps, d], out [rows, n_q, maps, dv], key pool [pages, n_kv * maps, page, d].
+static AttnLayout map_layout(int n_q, int n_kv, int d, int dv, int maps, int chunk) {
     AttnLayout lay;
-    lay.q_ts = (long long)n_q * maps * d; lay.q_hs = (long long)maps * d; lay.q_o = (long long)m * d;
-    lay.o_ts = (long long)n_q * maps * dv; lay.o_hs = (long long)maps * dv; lay.o_o = (long long)m * dv;
-    lay.n_kh = n_kv * maps; lay.k_mul = maps; lay.k_add = m; lay.chunk = chunk;
+    lay.q_ts = (long long)n_q * maps * d; lay.q_hs = (long long)maps * d; lay.q_o = 0;
+    lay.o_ts = (long long)n_q * maps * dv; lay.o_hs = (long long)maps * dv; lay.o_o = 0;
+    lay.n_kh = n_kv * maps; lay.k_mul = maps; lay.k_add = 0; lay.chunk = chunk; lay.maps = maps;
     return lay;
 }
 
@@ -589,10 +595,10 @@ static int prefill_bf16_layout(const void* q, const void* k_pool, const void* v_
                                int page_size, int max_pages, int n_pool_pages, int window, float scale,
                                AttnLayout lay, void* stream) {
     if (int rc = check_common("gi_attention_prefill_bf16", n_q, n_kv, d, page_size, max_pages, window)) return rc;
-    GI_REQUIRE(n_tiles >= 0 && n_q <= 65535, "gi_attention_prefill_bf16: tile or head count");
+    GI_REQUIRE(n_tiles >= 0 && (long long)n_q * lay.maps <= 65535, "gi_attention_prefill_bf16: tile or head count");
     if (n_tiles == 0) return 0;
     const float scale_log2 = scale * 1.4426950408889634f;
-    dim3 grid(n_tiles, n_q);
+    dim3 grid(n_tiles, n_q * lay.maps);
 #define CALL(DK, DV)                                                                                           \
     {                                                                                                          \
         const size_t smem = ((size_t)(AT_BM + 2 * AT_BN) * (DK + 8) + (size_t)2 * AT_BN * (DV + 8)) * sizeof(bf16); \
@@ -616,18 +622,15 @@ extern "C" int gi_attention_prefill_bf16(const void* q, const void* k_pool, cons
 }
 
 // The general prompt kernel: keys of d and values of dv, `maps` softmax maps per head over the same values (q
-// [rows, n_q, maps, d], out [rows, n_q, maps, dv], the key pool [pages, n_kv * maps, page, d]: one launch per map),
+// [rows, n_q, maps, d], out [rows, n_q, maps, dv], the key pool [pages, n_kv * maps, page, d]; one launch),
 // and `chunk` (0: none).
 extern "C" int gi_attention_prefill_masked_bf16(const void* q, const void* k_pool, const void* v_pool,
                                                 const int* block_table, const int* tiles, int n_tiles, void* out, int n_q,
                                                 int n_kv, int d, int dv, int page_size, int max_pages, int n_pool_pages,
                                                 int window, int chunk, int maps, float scale, void* stream) {
     GI_REQUIRE(maps >= 1 && chunk >= 0, "gi_attention_prefill_masked_bf16: %d maps, chunk %d", maps, chunk);
-    for (int m = 0; m < maps; ++m)
-        if (int rc = prefill_bf16_layout(q, k_pool, v_pool, block_table, tiles, n_tiles, out, n_q, n_kv, d, dv, page_size,
-                                         max_pages, n_pool_pages, window, scale,
-                                         map_layout(n_q, n_kv, d, dv, maps, m, chunk), stream)) return rc;
-    return 0;
+    return prefill_bf16_layout(q, k_pool, v_pool, block_table, tiles, n_tiles, out, n_q, n_kv, d, dv, page_size,
+                               max_pages, n_pool_pages, window, scale, map_layout(n_q, n_kv, d, dv, maps, chunk), stream);
 }
 
 static int decode_bf16_layout(const void* q, const void* k_pool, const void* v_pool, const int* block_table,
@@ -637,11 +640,11 @@ static int decode_bf16_layout(const void* q, const void* k_pool, const void* v_p
                               void* stream) {
     if (int rc = check_common("gi_attention_decode_bf16", n_q, n_kv, d, page_size, max_pages, window)) return rc;
     GI_REQUIRE(n_q / n_kv <= 16, "gi_attention_decode_bf16: %d query heads per key/value head; this kernel takes up to 16", n_q / n_kv);
-    GI_REQUIRE(n_splits >= 1 && n_splits <= 65535 && n_kv <= 65535 && n_seqs >= 0 && n_seqs <= 65535,
+    GI_REQUIRE(n_splits >= 1 && n_splits <= 65535 && (long long)n_kv * lay.maps <= 65535 && n_seqs >= 0 && n_seqs <= 65535,
                "gi_attention_decode_bf16: %d slices, %d key/value heads, %d sequences", n_splits, n_kv, n_seqs);
     if (n_seqs == 0) return 0;
     const float scale_log2 = scale * 1.4426950408889634f;
-    dim3 grid(n_splits, n_kv, n_seqs);
+    dim3 grid(n_splits, n_kv * lay.maps, n_seqs);
     const int cq = strided_out ? n_q : 0;
 #define CALL(DK, DV)                                                                                           \
     {                                                                                                          \
@@ -652,8 +655,8 @@ static int decode_bf16_layout(const void* q, const void* k_pool, const void* v_p
         gi_launch(decode_splitkv_kernel<DK, DV>, grid, dim3(AT_THREADS), smem, (cudaStream_t)stream,           \
             (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table, tok_pos, tok_slot, part_o,  \
             part_ml, n_q, n_kv, page_size, max_pages, n_pool_pages, window, scale_log2, n_splits, lay);        \
-        gi_launch(decode_combine_kernel<DV>, dim3(n_seqs * n_q), dim3(DV < 128 ? (DV < 32 ? 32 : DV) : 128), 0, (cudaStream_t)stream,  \
-            part_o, part_ml, (bf16*)out, n_splits, cq, lay.o_ts, lay.o_hs, lay.o_o);                           \
+        gi_launch(decode_combine_kernel<DV>, dim3(n_seqs * n_q * lay.maps), dim3(DV < 128 ? (DV < 32 ? 32 : DV) : 128), 0, (cudaStream_t)stream,  \
+            part_o, part_ml, (bf16*)out, n_splits, cq, lay.o_ts, lay.o_hs, lay.o_o, lay.maps);                 \
     }
     AT_DISPATCH_DD(d, dv, CALL)
 #undef CALL
@@ -672,18 +675,16 @@ extern "C" int gi_attention_decode_bf16(const void* q, const void* k_pool, const
 }
 
 // The general decode kernel: as gi_attention_prefill_masked_bf16, for one token per sequence.  Scratch as above with
-// dv for d (used by one map after the other).
+// dv for d and maps * n_q for n_q.
 extern "C" int gi_attention_decode_masked_bf16(const void* q, const void* k_pool, const void* v_pool,
                                                const int* block_table, const int* tok_pos, const int* tok_slot, void* out,
                                                float* part_o, float* part_ml, int n_seqs, int n_q, int n_kv, int d, int dv,
                                                int page_size, int max_pages, int n_pool_pages, int window, int chunk,
                                                int maps, float scale, int n_splits, void* stream) {
     GI_REQUIRE(maps >= 1 && chunk >= 0, "gi_attention_decode_masked_bf16: %d maps, chunk %d", maps, chunk);
-    for (int m = 0; m < maps; ++m)
-        if (int rc = decode_bf16_layout(q, k_pool, v_pool, block_table, tok_pos, tok_slot, out, part_o, part_ml, n_seqs,
-                                        n_q, n_kv, d, dv, page_size, max_pages, n_pool_pages, window, scale, n_splits,
-                                        map_layout(n_q, n_kv, d, dv, maps, m, chunk), true, stream)) return rc;
-    return 0;
+    return decode_bf16_layout(q, k_pool, v_pool, block_table, tok_pos, tok_slot, out, part_o, part_ml, n_seqs,
+                              n_q, n_kv, d, dv, page_size, max_pages, n_pool_pages, window, scale, n_splits,
+                              map_layout(n_q, n_kv, d, dv, maps, chunk), true, stream);
 }
 
 // Merges the slices' partial results of a split-KV decode kernel (this file's or the tcgen05 one):
@@ -696,7 +697,7 @@ extern "C" int gi_attention_decode_combine(const float* part_o, const float* par
     if (rows == 0) return 0;
 #define CALL(DD)                                                                                                 \
     gi_launch(decode_combine_kernel<DD>, dim3(rows), dim3(DD < 128 ? (DD < 32 ? 32 : DD) : 128), 0, (cudaStream_t)stream, \
-              part_o, part_ml, (bf16*)out, n_splits, 0, 0LL, 0LL, 0LL);
+              part_o, part_ml, (bf16*)out, n_splits, 0, 0LL, 0LL, 0LL, 1);
     AT_DISPATCH_D(d, CALL)
 #undef CALL
     return gi_check_launch("gi_attention_decode_combine");

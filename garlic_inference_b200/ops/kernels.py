@@ -908,7 +908,6 @@ def attention_prefill_masked_bf16(q: torch.Tensor, k_pool: torch.Tensor, v_pool:
                                              q_tiles.shape[0], _ptr(out), rows // maps, n_kv, d, dv, page_size,
                                              block_table.shape[1], n_pages, int(window or 0), int(chunk or 0), int(maps),
                                              float(scale), _stream()), l)
-    counters.launches += maps - 1
     return out
 
 
@@ -923,15 +922,15 @@ def attention_decode_masked_bf16(q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
         _dense(t, name, torch.int32)
     n, rows, d, dv, n_pages, n_kv, page_size = _masked_shapes(q, k_pool, v_pool, maps)
     heads = rows // maps
-    n_splits = n_splits or decode_splits(n, n_kv)
+    n_splits = n_splits or decode_splits(n, n_kv * maps)
     out = torch.empty((n, rows * dv), dtype=q.dtype, device=q.device)
-    part_o = torch.empty((n * heads * n_splits * dv,), dtype=torch.float32, device=q.device)
-    part_ml = torch.empty((n * heads * n_splits * 2,), dtype=torch.float32, device=q.device)
+    part_o = torch.empty((n * rows * n_splits * dv,), dtype=torch.float32, device=q.device)
+    part_ml = torch.empty((n * rows * n_splits * 2,), dtype=torch.float32, device=q.device)
     check(l.gi_attention_decode_masked_bf16(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), _ptr(tok_pos),
                                             _ptr(tok_slot), _ptr(out), _ptr(part_o), _ptr(part_ml), n, heads, n_kv, d, dv,
                                             page_size, block_table.shape[1], n_pages, int(window or 0), int(chunk or 0),
                                             int(maps), float(scale), n_splits, _stream()), l)
-    counters.launches += 2 * maps - 1
+    counters.launches += 1                                   # the combine kernel
     return out
 
 
