@@ -316,13 +316,57 @@ delta_scan_kernel(const float* __restrict__ qkv, long long ldq, int q_off, int k
 #pragma unroll
         for (int e = 0; e < R; ++e) S[e] = 0.f;
     }
+    // Each warp stages tokens warp, warp + W, ... of a chunk (W warps).  When the rows allow 16-byte loads, the raw
+    // values of the NEXT chunk's tokens are asked for into registers before this chunk's tokens are walked, so that
+    // the walk hides their latency; what is done with them, and in which order, is the same either way.
+    constexpr int TPW = TC / (SCAN_THREADS / 32);
+    constexpr int NQ = (DP / 4 + 31) / 32;                 // 16-byte pieces of q (and of k) per lane and token
+    constexpr int NA = CH ? (DP + 31) / 32 : 1;            // decay logits per lane and token
+    float4 pq[TPW][NQ], pk[TPW][NQ];
+    float pv[TPW], pa[TPW][NA], pb[TPW], dtc[NA];
+#pragma unroll
+    for (int n = 0; n < NA; ++n) {
+        const int c = lane + 32 * n;
+        dtc[n] = (CH && c < d) ? load_w(dt_bias, p_dtype, h * d + c) : 0.f;
+    }
+    auto fetch = [&](int t0) {
+        const int tc = min(TC, len - t0);
+#pragma unroll
+        for (int i = 0; i < TPW; ++i) {
+            const int t = warp + (SCAN_THREADS / 32) * i;
+            if (t >= tc) continue;
+            const float* row = qkv + (size_t)(start + t0 + t) * ldq;
+            const float* abr = ab + (size_t)(start + t0 + t) * ldab;
+            const float* alr = al + (size_t)(start + t0 + t) * ldal;
+#pragma unroll
+            for (int n = 0; n < NQ; ++n) {
+                const int c4 = lane + 32 * n;
+                pq[i][n] = make_float4(0.f, 0.f, 0.f, 0.f);
+                pk[i][n] = pq[i][n];
+                if (c4 < DP / 4 && c4 * 4 < d) {
+                    pq[i][n] = *reinterpret_cast<const float4*>(row + q_off + kh * d + c4 * 4);
+                    pk[i][n] = *reinterpret_cast<const float4*>(row + k_off + kh * d + c4 * 4);
+                }
+            }
+            pv[i] = v0 + lane < dv ? row[v_off + h * dv + v0 + lane] : 0.f;
+            if (CH) {
+#pragma unroll
+                for (int n = 0; n < NA; ++n) {
+                    const int c = lane + 32 * n;
+                    pa[i][n] = c < d ? alr[a_off + h * d + c] : 0.f;
+                }
+            } else {
+                pa[i][0] = lane == 0 ? alr[a_off + h] : 0.f;
+            }
+            pb[i] = lane == 0 ? abr[b_off + h] : 0.f;
+        }
+    };
+    if (vec) fetch(0);
     for (int t0 = 0; t0 < len; t0 += TC) {
         const int tc = min(TC, len - t0);
         __syncthreads();
-        // each warp stages tokens warp, warp + 4, ...: first the raw q, k and v of all its tokens (independent
-        // loads, 16 bytes at a time when the rows allow it), then q and k as unit vectors (sum of squares: a
+        // raw q, k and v of a warp's tokens into shared memory, then q and k as unit vectors (sum of squares: a
         // lane's elements in order, then a tree over the lanes)
-        constexpr int TPW = TC / (SCAN_THREADS / 32);
         float sq[TPW], sk[TPW];
 #pragma unroll
         for (int i = 0; i < TPW; ++i) {
@@ -330,13 +374,14 @@ delta_scan_kernel(const float* __restrict__ qkv, long long ldq, int q_off, int k
             sq[i] = 0.f; sk[i] = 0.f;
             if (t >= tc) continue;
             const float* row = qkv + (size_t)(start + t0 + t) * ldq;
+            const float* abr = ab + (size_t)(start + t0 + t) * ldab;
+            const float* alr = al + (size_t)(start + t0 + t) * ldal;
             if (vec) {
-                for (int c4 = lane; c4 < DP / 4; c4 += 32) {
-                    float4 qv = make_float4(0.f, 0.f, 0.f, 0.f), kv = qv;
-                    if (c4 * 4 < d) {
-                        qv = *reinterpret_cast<const float4*>(row + q_off + kh * d + c4 * 4);
-                        kv = *reinterpret_cast<const float4*>(row + k_off + kh * d + c4 * 4);
-                    }
+#pragma unroll
+                for (int n = 0; n < NQ; ++n) {
+                    const int c4 = lane + 32 * n;
+                    if (c4 >= DP / 4) continue;
+                    const float4 qv = pq[i][n], kv = pk[i][n];
                     *reinterpret_cast<float4*>(&q_s[t][c4 * 4]) = qv;
                     *reinterpret_cast<float4*>(&k_s[t][c4 * 4]) = kv;
                     sq[i] = fmaf(qv.x, qv.x, sq[i]); sq[i] = fmaf(qv.y, qv.y, sq[i]);
@@ -344,17 +389,27 @@ delta_scan_kernel(const float* __restrict__ qkv, long long ldq, int q_off, int k
                     sk[i] = fmaf(kv.x, kv.x, sk[i]); sk[i] = fmaf(kv.y, kv.y, sk[i]);
                     sk[i] = fmaf(kv.z, kv.z, sk[i]); sk[i] = fmaf(kv.w, kv.w, sk[i]);
                 }
-            } else {
-                for (int c = lane; c < DP; c += 32) {
-                    const float qv = c < d ? row[q_off + kh * d + c] : 0.f;
-                    const float kv = c < d ? row[k_off + kh * d + c] : 0.f;
-                    q_s[t][c] = qv; k_s[t][c] = kv;
-                    sq[i] = fmaf(qv, qv, sq[i]); sk[i] = fmaf(kv, kv, sk[i]);
+                v_s[t][lane] = pv[i];
+                if (CH) {
+#pragma unroll
+                    for (int n = 0; n < NA; ++n) {
+                        const int c = lane + 32 * n;
+                        if (c < DP) gc_s[t][c] = c < d ? expf(-rate * rc_softplus(pa[i][n] + dtc[n])) : 1.f;
+                    }
                 }
+                if (lane == 0) {
+                    if (!CH) g_s[t] = expf(-rate * rc_softplus(pa[i][0] + dt));
+                    b_s[t] = rc_sigmoid(pb[i]);
+                }
+                continue;
+            }
+            for (int c = lane; c < DP; c += 32) {
+                const float qv = c < d ? row[q_off + kh * d + c] : 0.f;
+                const float kv = c < d ? row[k_off + kh * d + c] : 0.f;
+                q_s[t][c] = qv; k_s[t][c] = kv;
+                sq[i] = fmaf(qv, qv, sq[i]); sk[i] = fmaf(kv, kv, sk[i]);
             }
             v_s[t][lane] = v0 + lane < dv ? row[v_off + h * dv + v0 + lane] : 0.f;
-            const float* abr = ab + (size_t)(start + t0 + t) * ldab;
-            const float* alr = al + (size_t)(start + t0 + t) * ldal;
             if (CH) {
                 for (int c = lane; c < DP; c += 32)
                     gc_s[t][c] = c < d ? expf(-rate * rc_softplus(alr[a_off + h * d + c] + load_w(dt_bias, p_dtype, h * d + c))) : 1.f;
@@ -372,6 +427,7 @@ delta_scan_kernel(const float* __restrict__ qkv, long long ldq, int q_off, int k
             for (int c = lane; c < DP; c += 32) { q_s[t][c] *= iq; k_s[t][c] *= ik; }
         }
         __syncthreads();
+        if (vec && t0 + TC < len) fetch(t0 + TC);
         for (int t = 0; t < tc; ++t) {
             const float g = CH ? 1.f : g_s[t];
             float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;     // four chains instead of one of R dependent steps

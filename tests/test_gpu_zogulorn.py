@@ -401,6 +401,38 @@ def test_tensor_core_attention_with_chunks_two_maps_and_values_of_another_size(d
                 torch.testing.assert_close(one[s, :, mp], want[-1], rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("chunk", [1, 64, 100, 128, 200, 1000])
+def test_tcgen05_prompt_attention_with_chunks(chunk):
+    """The tcgen05 prompt kernel (heads of 128, pages of 64) with chunks smaller than, equal to and larger than its
+    tiles of 64 keys and 128 queries, for a sequence that starts and one that goes on from cached keys."""
+    from garlic_inference_b200.ops import kernels
+    from garlic_inference_b200.parts import StepShape
+    from garlic_inference_b200.parts.attention import query_runs
+    torch.manual_seed(5)
+    H, G, d, page = 4, 2, 128, 64
+    lens, past = [300, 150], [0, 210]
+    k_pool = (torch.randn(16, G, page, d, device="cuda") * 0.5).bfloat16()
+    v_pool = torch.randn(16, G, page, d, device="cuda").bfloat16()
+    table = torch.full((2, 8), -1, dtype=torch.int32, device="cuda")
+    table[0, :5] = torch.tensor([9, 2, 11, 4, 13], dtype=torch.int32)
+    table[1, :6] = torch.tensor([0, 7, 1, 8, 3, 15], dtype=torch.int32)
+    n = sum(lens)
+    q = torch.randn(n, H, d, device="cuda").bfloat16()
+    runs = torch.from_numpy(query_runs(StepShape([0, 1], [0, 300], lens, past, False), 128)).cuda()
+    got = kernels.attention_prefill_tcgen05(q, k_pool, v_pool, table, runs, 0.1, 0, rows_covered=True, chunk=chunk)
+    kernels.check_bounded_waits(torch.device("cuda", 0))
+    got = got.float().cpu().view(n, H, d)
+    for s, (start, m, p0) in enumerate(zip([0, 300], lens, past)):
+        T = p0 + m
+        pages = table[s, :-(-T // page)].long()
+        keys = k_pool[pages].float().cpu().permute(0, 2, 1, 3).reshape(-1, G, d)[:T]
+        vals = v_pool[pages].float().cpu().permute(0, 2, 1, 3).reshape(-1, G, d)[:T]
+        qs = torch.zeros(T, H, d)
+        qs[p0:] = q[start:start + m].float().cpu()
+        want = plain.attend(qs, keys, vals, 0.1, plain.chunk_mask(T, chunk))[p0:]
+        torch.testing.assert_close(got[start:start + m], want, rtol=2e-2, atol=2e-2)
+
+
 def test_delta_scan_with_a_decay_per_key_channel_and_plain_filters():
     from garlic_inference_b200.ops import kernels
     from garlic_inference_b200.parts.linear_attention import scan_state_floats
