@@ -175,6 +175,21 @@ def test_long_decoding(name, dtype, model, folder):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["moe", "mix"])
+def test_a_dozen_requests_decode_together(name, dtype, model, folder):
+    """Twelve unequal requests start together and decode together through a recorded step of 16 rows (four of them
+    padding): the routed feed-forward then runs expert by expert inside the recording, the attention kernels see
+    padding rows, and requests leave one after the other."""
+    m = model(name, dtype, max_tokens=2048, page_size=16, max_slots=12)
+    reqs = _requests(name, [31 + 3 * i for i in range(12)], seed=21)
+    want, own = tz.plain_pair(folder(name), reqs)
+    got = tiny.run_trace_in_process(m, tiny.trace_batched(reqs, [list(reqs)], prompt_frac=0.5))
+    tiny.assert_covers(got, reqs)
+    tz.judge(got, want, own, dtype, f"twelve together {name} {dtype}")
+    assert m.engine.graphs is not None and 16 in m.engine.graphs._graphs
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_greedy_generation_through_the_entry_point(dtype, model, folder):
     m = model("mix", dtype, max_tokens=512, page_size=16, max_slots=3)
     prompts = list(_requests("mix", [9, 1, 30, 17, 5], seed=10).values())
