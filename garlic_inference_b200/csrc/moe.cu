@@ -6,6 +6,8 @@
 //                      falling order, and the softmax over those chosen logits alone
 //   gi_moe_up          a[t, j, :] = act( W_up[e_tj] x_t )          act: the square of relu (0) or silu (1)
 //   gi_moe_down        part[t, j, :] = W_down[e_tj] a[t, j, :]
+//   gi_moe_group       the (token, choice) pairs in the order of their experts: each pair's row, each expert's last
+//                      row, and the tokens' vectors gathered into that order (a stable counting sort)
 //   gi_moe_combine     y[t, :] = sum_j w_tj buf[where[t, j], :]   in the router's order of j: over gi_moe_down's
 //                      rows (where = none: row t top + j), or over rows that a grouped product wrote expert by expert
 //
@@ -243,6 +245,123 @@ extern "C" int gi_moe_down(const void* a, const void* w_down, const int* idx, vo
         GI_REQUIRE(false, "gi_moe_down: activation dtype %d", act_dtype);
     }
     return gi_check_launch("gi_moe_down");
+}
+
+// ------------------------------------------------------------------ (token, choice) pairs in the order of their experts
+// For the grouped products: pair p = t top + j goes to row where[p] of a matrix whose rows are sorted by expert, the
+// pairs of one expert in the order of p (a counting sort, stable, so the layout does not depend on timing).
+//   moe_count    every block counts its MOE_SEG pairs per expert
+//   moe_offsets  one block: where each expert's rows end (`ends`), and where each block's pairs of each expert start
+//   moe_place    a pair's row: its block's start for the expert + the pairs of that expert before it in the block
+//   moe_gather   rows[where[p]] = x[p / top]
+#define MOE_SEG 1024
+
+__global__ void __launch_bounds__(MOE_SEG)
+moe_count_kernel(const int* __restrict__ idx, int n_pairs, int E, int* __restrict__ block_counts) {
+    gi_pdl_start();
+    extern __shared__ int cnt[];                        // E
+    for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    const int p = blockIdx.x * MOE_SEG + threadIdx.x;
+    if (p < n_pairs) {
+        const int e = idx[p];
+        if (e >= 0 && e < E) atomicAdd(&cnt[e], 1);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) block_counts[(size_t)blockIdx.x * E + e] = cnt[e];
+}
+
+// block_counts [n_blocks, E] become each block's first row for each expert; ends [E].
+__global__ void moe_offsets_kernel(int* __restrict__ block_counts, int n_blocks, int E, int* __restrict__ ends) {
+    gi_pdl_start();
+    extern __shared__ int total[];                      // E totals, then E starts
+    int* first = total + E;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int t = 0;
+        for (int b = 0; b < n_blocks; ++b) t += block_counts[(size_t)b * E + e];
+        total[e] = t;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < E; ++e) { first[e] = at; at += total[e]; ends[e] = at; }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int at = first[e];
+        for (int b = 0; b < n_blocks; ++b) {
+            const int c = block_counts[(size_t)b * E + e];
+            block_counts[(size_t)b * E + e] = at;
+            at += c;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(MOE_SEG)
+moe_place_kernel(const int* __restrict__ idx, int n_pairs, int E, const int* __restrict__ block_first,
+                 int* __restrict__ where) {
+    gi_pdl_start();
+    extern __shared__ int wc[];                         // [32 warps][E]: a warp's pairs per expert, then their prefix
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    for (int i = threadIdx.x; i < n_warps * E; i += blockDim.x) wc[i] = 0;
+    __syncthreads();
+    const int p = blockIdx.x * MOE_SEG + threadIdx.x;
+    int e = p < n_pairs ? idx[p] : -1;
+    if (e < 0 || e >= E) e = -1;
+    const unsigned same = __match_any_sync(0xffffffffu, e);
+    const int rank = __popc(same & ((1u << lane) - 1u));
+    if (e >= 0 && rank == 0) wc[warp * E + e] = __popc(same);
+    __syncthreads();
+    for (int x = threadIdx.x; x < E; x += blockDim.x) {             // exclusive prefix over the warps, per expert
+        int at = 0;
+        for (int w = 0; w < n_warps; ++w) { const int c = wc[w * E + x]; wc[w * E + x] = at; at += c; }
+    }
+    __syncthreads();
+    if (e >= 0) where[p] = block_first[(size_t)blockIdx.x * E + e] + wc[warp * E + e] + rank;
+    else if (p < n_pairs) where[p] = 0;
+}
+
+template <typename T>
+__global__ void moe_gather_kernel(const T* __restrict__ x, long long ldx, const int* __restrict__ where, int top,
+                                  T* __restrict__ rows, int hidden, int vec) {
+    gi_pdl_start();
+    const int p = blockIdx.x;
+    const T* src = x + (size_t)(p / top) * ldx;
+    T* dst = rows + (size_t)where[p] * hidden;
+    if (vec) {
+        const int n16 = hidden * (int)sizeof(T) / 16;
+        for (int i = threadIdx.x; i < n16; i += blockDim.x)
+            reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+// idx [n_rows, top] -> where [n_rows * top], ends [E], rows [n_rows * top, hidden] (x's rows in the experts' order).
+// scratch: int32 [ceil(n_rows top / 1024) * E].
+extern "C" int gi_moe_group(const int* idx, const void* x, long long ldx, int act_dtype, int* where, int* ends, void* rows,
+                            int* scratch, int n_rows, int top, int E, int hidden, void* stream) {
+    GI_REQUIRE(n_rows >= 0 && top > 0 && E > 0 && hidden > 0 && ldx >= hidden, "gi_moe_group: sizes");
+    GI_REQUIRE(E <= 1024, "gi_moe_group: %d experts (at most 1024)", E);
+    const long long n_pairs = (long long)n_rows * top;
+    GI_REQUIRE(n_pairs < (1LL << 31), "gi_moe_group: %lld pairs", n_pairs);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (n_rows == 0) return 0;
+    const int n_blocks = (int)((n_pairs + MOE_SEG - 1) / MOE_SEG);
+    gi_launch(moe_count_kernel, dim3(n_blocks), dim3(MOE_SEG), (size_t)E * sizeof(int), s, idx, (int)n_pairs, E, scratch);
+    gi_launch(moe_offsets_kernel, dim3(1), dim3(256), (size_t)2 * E * sizeof(int), s, scratch, n_blocks, E, ends);
+    const size_t place_smem = (size_t)(MOE_SEG / 32) * E * sizeof(int);
+    if (place_smem > 48 * 1024) { int rc = gi_reserve_smem((const void*)moe_place_kernel, place_smem, "gi_moe_group"); if (rc) return rc; }
+    gi_launch(moe_place_kernel, dim3(n_blocks), dim3(MOE_SEG), place_smem, s, idx, (int)n_pairs, E, (const int*)scratch, where);
+    const int esz = act_dtype == GI_DTYPE_F32 ? 4 : 2;
+    const int vec = ((long long)hidden * esz) % 16 == 0 && (ldx * esz) % 16 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)rows % 16 == 0;
+    if (act_dtype == GI_DTYPE_F32)
+        gi_launch(moe_gather_kernel<float>, dim3((unsigned)n_pairs), dim3(128), 0, s, (const float*)x, ldx, (const int*)where, top, (float*)rows, hidden, vec);
+    else if (act_dtype == GI_DTYPE_BF16)
+        gi_launch(moe_gather_kernel<bf16>, dim3((unsigned)n_pairs), dim3(128), 0, s, (const bf16*)x, ldx, (const int*)where, top, (bf16*)rows, hidden, vec);
+    else
+        GI_REQUIRE(false, "gi_moe_group: activation dtype %d", act_dtype);
+    return gi_check_launch("gi_moe_group");
 }
 
 // ------------------------------------------------------------------ the weighted sum over rows written expert by expert

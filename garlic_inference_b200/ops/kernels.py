@@ -402,6 +402,24 @@ def moe_rowwise(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, idx: 
     return moe_combine(part, None, wt)
 
 
+def moe_group(idx: torch.Tensor, x: torch.Tensor, n_experts: int):
+    """The (token, choice) pairs of idx [n, top] in the order of their experts (stable): returns (where int32 [n, top],
+    each pair's row; ends int32 [n_experts], each expert's last row + 1; rows [n * top, hidden], x's rows in that
+    order)."""
+    l = require_gpu()
+    _dense(idx, "idx", torch.int32), _rows(x, "x")
+    n, top = idx.shape
+    hidden = x.shape[1]
+    where = torch.empty((n, top), dtype=torch.int32, device=x.device)
+    ends = torch.empty((n_experts,), dtype=torch.int32, device=x.device)
+    rows = torch.empty((n * top, hidden), dtype=x.dtype, device=x.device)
+    scratch = torch.empty((-(-(n * top) // 1024) * n_experts,), dtype=torch.int32, device=x.device)
+    check(l.gi_moe_group(_ptr(idx), _ptr(x), x.stride(0), code(x.dtype), _ptr(where), _ptr(ends), _ptr(rows), _ptr(scratch),
+                         n, top, n_experts, hidden, _stream()), l)
+    counters.launches += 3
+    return where, ends, rows
+
+
 def moe_combine(buf: torch.Tensor, where: Optional[torch.Tensor], wt: torch.Tensor) -> torch.Tensor:
     """y[t] = sum_j wt[t, j] buf[where[t, j]] (float32 sums in the order of j); without `where`: row t * top + j."""
     l = require_gpu()

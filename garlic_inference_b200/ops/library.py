@@ -44,6 +44,7 @@ _SIGNATURES = {
     "gi_router_topk": ([P, L, I, I, P, P, I, P], I),
     "gi_moe_up": ([P, L, P, P, P, I, I, I, I, I, I, I, P], I),
     "gi_moe_down": ([P, P, P, P, I, I, I, I, I, I, P], I),
+    "gi_moe_group": ([P, P, L, I, P, P, P, P, I, I, I, I, P], I),
     "gi_moe_combine": ([P, P, P, P, I, I, I, I, P], I),
     "gi_causal_conv": ([P, L, I, I, P, I, I, P, L, P, P, I, I, I, P], I),
     "gi_gate_norm_add": ([P, L, P, L, P, I, P, I, P, P, I, I, I, F, P], I),

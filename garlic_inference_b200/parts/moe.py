@@ -8,7 +8,8 @@
 The experts' matrices are stacked at load time ([experts, ff, hidden] and [experts, hidden, ff]).  Two ways to
 run them.  A step of a few rows (a decode step; such a step may be recorded, so nothing may come back to the
 host): kernels that read the chosen experts' matrices only, a warp per matrix row, the experts taken from
-device memory.  More rows: the (token, choice) pairs are sorted by expert on the device, the experts run two
+device memory.  More rows: the (token, choice) pairs are put in the order of their experts by a counting sort on
+the device (which also gathers the tokens' vectors into that order), the experts run two
 matrix products over their own rows, and one kernel sums each token's `top` results with its weights in the
 router's order.  In bfloat16 the two products are the library's grouped product (`torch._grouped_mm`: the rows
 of every expert in one launch, the groups' ends read from device memory, nothing comes to the host); in float32,
@@ -53,7 +54,6 @@ class RoutedExperts(FeedForward):
         if self.activation not in ("relu_squared", "silu"):
             raise ValueError(f"expert activation {self.activation!r} is neither 'relu_squared' nor 'silu'")
         self.w_router = load("router").to(torch.float32)
-        self._next_expert = torch.arange(1, self.E + 1, dtype=torch.int64, device=rt.device)
         names = [f"e{e}.up" for e in range(self.E)]
         dtype = load.dtype(*names, *(f"e{e}.down" for e in range(self.E)))
         self.w_up = torch.empty((self.E, self.ff, self.hidden), dtype=dtype, device=rt.device)
@@ -69,14 +69,8 @@ class RoutedExperts(FeedForward):
         grouped = self._grouped(x)
         if n <= ROWWISE_MAX_ROWS or self.activation != "relu_squared" or (ctx.captured and not grouped):
             return kernels.moe_rowwise(x, self.w_up, self.w_down, idx, wt, self.activation)
-        # expert by expert: pairs (token, choice) sorted by expert; `where` is each pair's row in that order
-        flat = idx.reshape(-1)
-        experts, order = torch.sort(flat.to(torch.int64), stable=True)
-        where = torch.empty_like(order)
-        where[order] = torch.arange(order.numel(), device=order.device)
-        # where each expert's rows end in the sorted order: the pairs whose expert is below e + 1
-        ends = torch.searchsorted(experts, self._next_expert).to(torch.int32)
-        rows = x.index_select(0, order // self.top)
+        # expert by expert: the pairs (token, choice) in the order of their experts; `where` is each pair's row
+        where, ends, rows = kernels.moe_group(idx, x, self.E)
         if grouped:
             a = kernels.relu_squared(torch._grouped_mm(rows, self.w_up.transpose(1, 2), offs=ends))
             buf = torch._grouped_mm(a, self.w_down.transpose(1, 2), offs=ends)
@@ -90,7 +84,7 @@ class RoutedExperts(FeedForward):
                     a = kernels.relu_squared(linear(rows[at:at + c], self.w_up[e]))
                     buf[at:at + c] = linear(a, self.w_down[e])
                     at += c
-        return kernels.moe_combine(buf.contiguous(), where.to(torch.int32).view(n, self.top), wt)
+        return kernels.moe_combine(buf.contiguous(), where, wt)
 
     def _grouped(self, x) -> bool:
         """Whether the library's grouped product takes these operands: bfloat16, rows of 16-byte multiples."""

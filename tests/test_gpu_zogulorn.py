@@ -297,6 +297,17 @@ def test_router_and_expert_kernels():
         y = (torch.relu(x.cpu() @ up[e].cpu().T) ** 2) @ down[e].cpu().T
         want += y * (wt.cpu() * (idx.cpu() == e)).sum(-1, keepdim=True)
     torch.testing.assert_close(kernels.moe_rowwise(x, up, down, idx, wt, "relu_squared").cpu(), want, rtol=1e-4, atol=1e-4)
+    for rows_n, experts in ((45, 7), (1500, 3), (700, 70)):       # one block of pairs, several, more experts than a warp
+        ids = torch.randint(0, experts, (rows_n, 2), device="cuda", dtype=torch.int32)
+        xs = torch.randn(rows_n, 24, device="cuda")
+        where, ends, rows = kernels.moe_group(ids, xs, experts)
+        flat = ids.reshape(-1).long().cpu()
+        order = torch.sort(flat, stable=True).indices
+        want_where = torch.empty_like(order)
+        want_where[order] = torch.arange(order.numel())
+        assert torch.equal(where.reshape(-1).long().cpu(), want_where), "pairs in the order of their experts, stable"
+        assert torch.equal(ends.long().cpu(), torch.cumsum(torch.bincount(flat, minlength=experts), 0))
+        assert torch.equal(rows.cpu(), xs.cpu()[order // 2])
     buf = torch.randn(n * top, hid, device="cuda")
     where = torch.randperm(n * top, device="cuda").to(torch.int32).view(n, top)
     got = kernels.moe_combine(buf, where, wt)
