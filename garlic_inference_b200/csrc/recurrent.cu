@@ -43,7 +43,8 @@ __device__ __forceinline__ int rows_before(const int* __restrict__ tok_slot, int
 template <typename T>
 __global__ void causal_conv_silu_kernel(const T* __restrict__ x, long long ldx, int C, const void* __restrict__ taps,
                                         int taps_dtype, int K, const float* __restrict__ state, long long state_stride,
-                                        const int* __restrict__ tok_slot, float* __restrict__ out, int act) {
+                                        const int* __restrict__ tok_slot, float* __restrict__ out, int act,
+                                        float* __restrict__ state_out) {
     gi_pdl_start();
     const int r = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
@@ -51,13 +52,19 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ x, long long ldx, 
     const int slot = tok_slot[r];
     const int have = slot < 0 ? 0 : rows_before(tok_slot, r, slot, K - 1);
     float acc = 0.f;
+    float seen[CONV_MAX_TAPS];                       // the inputs, oldest first (for the state when it is renewed here)
     for (int j = K - 1; j >= 0; --j) {               // oldest input first, whatever its source
         float xv = 0.f;
         if (j <= have) xv = to_f32(x[(size_t)(r - j) * ldx + c]);
         else if (slot >= 0) xv = state[(size_t)slot * state_stride + (size_t)(K - 1 + have - j) * C + c];
+        seen[K - 1 - j] = xv;
         acc = fmaf(load_w(taps, taps_dtype, c * K + (K - 1 - j)), xv, acc);
     }
     out[(size_t)r * C + c] = act ? rc_silu(acc) : acc;
+    // Steps in which every row is a sequence of its own (decode steps): the slot's state becomes its last K - 1 inputs
+    // here, by the one thread that read it, instead of in a launch of its own.
+    if (state_out && slot >= 0)
+        for (int m = 0; m < K - 1; ++m) state_out[(size_t)slot * state_stride + (size_t)m * C + c] = seen[m + 1];
 }
 
 template <typename T>
@@ -80,7 +87,8 @@ __global__ void conv_state_update_kernel(const T* __restrict__ x, long long ldx,
     for (int m = 0; m < K - 1; ++m) st[(size_t)m * C + c] = vals[m];
 }
 
-// `act` 1: silu of the filter's sum; 0: the sum itself.
+// `act` 1: silu of the filter's sum; 0: the sum itself.  update_state 2: the filter and the renewal of the state in
+// one launch, for steps in which no two rows belong to one sequence (the caller's promise).
 extern "C" int gi_causal_conv(const void* x, long long ldx, int act_dtype, int C, const void* taps, int taps_dtype,
                               int K, float* state, long long state_stride, const int* tok_slot, float* out,
                               int n_rows, int update_state, int act, void* stream) {
@@ -92,10 +100,10 @@ extern "C" int gi_causal_conv(const void* x, long long ldx, int act_dtype, int C
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_rows, (C + 127) / 128);
     if (act_dtype == GI_DTYPE_F32) {
-        if (!update_state) gi_launch(causal_conv_silu_kernel<float>, grid, dim3(128), 0, s, (const float*)x, ldx, C, taps, taps_dtype, K, (const float*)state, state_stride, tok_slot, out, act);
+        if (update_state != 1) gi_launch(causal_conv_silu_kernel<float>, grid, dim3(128), 0, s, (const float*)x, ldx, C, taps, taps_dtype, K, (const float*)state, state_stride, tok_slot, out, act, update_state == 2 && K > 1 ? state : (float*)nullptr);
         else if (K > 1) gi_launch(conv_state_update_kernel<float>, grid, dim3(128), 0, s, (const float*)x, ldx, C, K, state, state_stride, tok_slot, n_rows);
     } else if (act_dtype == GI_DTYPE_BF16) {
-        if (!update_state) gi_launch(causal_conv_silu_kernel<bf16>, grid, dim3(128), 0, s, (const bf16*)x, ldx, C, taps, taps_dtype, K, (const float*)state, state_stride, tok_slot, out, act);
+        if (update_state != 1) gi_launch(causal_conv_silu_kernel<bf16>, grid, dim3(128), 0, s, (const bf16*)x, ldx, C, taps, taps_dtype, K, (const float*)state, state_stride, tok_slot, out, act, update_state == 2 && K > 1 ? state : (float*)nullptr);
         else if (K > 1) gi_launch(conv_state_update_kernel<bf16>, grid, dim3(128), 0, s, (const bf16*)x, ldx, C, K, state, state_stride, tok_slot, n_rows);
     } else {
         GI_REQUIRE(false, "gi_causal_conv_silu: activation dtype %d", act_dtype);

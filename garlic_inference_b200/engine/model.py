@@ -14,7 +14,7 @@ from typing import Optional
 import torch
 
 from ..config.base import ModelPlan, PartSpec
-from ..parts import Runtime, StepContext, part_class
+from ..parts import Part, Runtime, StepContext, part_class
 from ..weights.loader import TensorWant, WeightError, device_dtype
 
 
@@ -174,7 +174,11 @@ class DecoderModel:
         yield self.embedding
         yield from self.positions.values()
         for b in self.blocks:
-            yield from (p for p in (b.mixer, b.feed_forward) if p is not None)
+            for p in (b.mixer, b.feed_forward):
+                if p is not None:
+                    yield p
+                    # a part put together from parts (two mixers side by side)
+                    yield from (v for v in vars(p).values() if isinstance(v, Part))
             yield from (v for v in vars(b).values() if hasattr(v, "add_norm") or hasattr(v, "logits"))
         yield self.final_norm
         yield self.head

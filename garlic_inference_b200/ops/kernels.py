@@ -505,16 +505,17 @@ def scan_state_floats(key_dim: int, value_dim: int) -> int:
 
 
 def causal_conv_silu(x: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, tok_slot: torch.Tensor,
-                     activation: str = "silu") -> torch.Tensor:
+                     activation: str = "silu", renew_state: bool = False) -> torch.Tensor:
     """silu (or, with activation "none", the plain sum) of the causal convolution over time of x [n, C] (rows may lie apart) with taps [C, K], the K-1 inputs
     before the step's first token of a sequence taken from `state` [slots, >= (K-1) C] (a view of float32 state
-    rows); returns float32 [n, C].  Call `conv_state_update` afterwards."""
+    rows); returns float32 [n, C].  Call `conv_state_update` afterwards, or pass `renew_state` when no two rows of
+    the step belong to one sequence (a decode step): the same launch then renews the state."""
     l = require_gpu()
     _rows(x, "x"), _dense(taps, "taps"), _rows(state, "state", torch.float32), _dense(tok_slot, "tok_slot", torch.int32)
     n, C = x.shape
     out = torch.empty((n, C), dtype=torch.float32, device=x.device)
     check(l.gi_causal_conv(_ptr(x), x.stride(0), code(x.dtype), C, _ptr(taps), code(taps.dtype), taps.shape[1],
-                           _ptr(state), state.stride(0), _ptr(tok_slot), _ptr(out), n, 0,
+                           _ptr(state), state.stride(0), _ptr(tok_slot), _ptr(out), n, 2 if renew_state else 0,
                            {"none": 0, "silu": 1}[activation], _stream()), l)
     return out
 

@@ -105,8 +105,9 @@ class GatedDeltaRule(Mixer):
         proj = linear(x, self.w_in)
         conv_in = proj[:, :self.C]
         conv_state = cache.state[:, self.scan_floats:]
-        qkv = kernels.causal_conv_silu(conv_in, self.taps, conv_state, ctx.tok_slot)
-        kernels.conv_state_update(conv_in, self.K, conv_state, ctx.tok_slot)
+        qkv = kernels.causal_conv_silu(conv_in, self.taps, conv_state, ctx.tok_slot, renew_state=ctx.all_single)
+        if not ctx.all_single:
+            kernels.conv_state_update(conv_in, self.K, conv_state, ctx.tok_slot)
         ba = linear(x, self.w_ba, out_dtype=torch.float32)
         decay = None
         if self.decay_rank:                          # the decay's logits stay float32 out of the second thin product

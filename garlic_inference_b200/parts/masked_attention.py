@@ -151,8 +151,10 @@ class MaskedAttention(Mixer):
         if self.K:
             conv_in = proj[:, :self.C]
             if self.K > 1:
-                src = kernels.causal_conv_silu(conv_in, self.taps, cache.state, ctx.tok_slot, activation="none")
-                kernels.conv_state_update(conv_in, self.K, cache.state, ctx.tok_slot)
+                src = kernels.causal_conv_silu(conv_in, self.taps, cache.state, ctx.tok_slot, activation="none",
+                                               renew_state=ctx.all_single)
+                if not ctx.all_single:
+                    kernels.conv_state_update(conv_in, self.K, cache.state, ctx.tok_slot)
             else:                                     # one tap: a factor per channel, no state
                 if self._no_state is None:
                     self._no_state = torch.zeros((cache.kv.block_table.shape[0] + 1, 4), dtype=torch.float32, device=x.device)

@@ -60,8 +60,7 @@ class ParallelMixers(Mixer):
                 self.left.w_o.dtype == self.right.w_o.dtype and self.left.w_o.shape[1] % 8 == 0:
             self.k_left = self.left.w_o.shape[1]
             self.w_o = torch.cat([self.left.w_o, self.right.w_o], dim=1).contiguous()
-            self.left.w_o = self.w_o[:, :self.k_left]            # views: the sides' own copies are let go
-            self.right.w_o = self.w_o[:, self.k_left:]
+            self.left.w_o = self.right.w_o = None                # the sides' own copies are let go: only pre_output runs
 
     @property
     def graph_safe(self):
