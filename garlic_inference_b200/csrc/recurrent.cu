@@ -21,6 +21,9 @@
 // (P = 4 / 8 / 16): a prompt of 2,048 tokens 0.91 / 0.71 / 0.70 ms (decay) and 1.61 / 1.23 / 1.04 ms (delta rule); a
 // whole decode step of 64 sequences 1.72 / 1.80 / 1.89 ms.  P never depends on the batch or the cut, so a
 // position's bits do not either.
+// The delta rule's scan asks for the next chunk's inputs (into registers) before it walks the present chunk's
+// tokens, when the rows allow 16-byte loads: a prompt of 2,048 tokens, 16 heads of 128 x 128, 1.20 -> 0.77 ms with a
+// decay per head and 1.68 -> 1.07 ms with one per key channel; what is computed, and in which order, is the same.
 // State rows are laid out [head][value column][key, padded to R P] so that a warp's loads and stores are
 // whole runs of 16 P bytes.  NikolayBlagoev/garlic-inference has no recurrent mixer.
 #include "common.cuh"

@@ -9,13 +9,12 @@ The experts' matrices are stacked at load time ([experts, ff, hidden] and [exper
 run them.  A step of a few rows (a decode step; such a step may be recorded, so nothing may come back to the
 host): kernels that read the chosen experts' matrices only, a warp per matrix row, the experts taken from
 device memory.  More rows: the (token, choice) pairs are put in the order of their experts by a counting sort on
-the device (which also gathers the tokens' vectors into that order), the experts run two
-matrix products over their own rows, and one kernel sums each token's `top` results with its weights in the
-router's order.  In bfloat16 the two products are the library's grouped product (`torch._grouped_mm`: the rows
+the device (which also gathers the tokens' vectors into that order), the experts run two matrix products over
+their own rows, and one kernel sums each token's `top` results with its weights in the router's order.  In bfloat16 the two products are the library's grouped product (`torch._grouped_mm`: the rows
 of every expert in one launch, the groups' ends read from device memory, nothing comes to the host); in float32,
 or where the library has no grouped product, the counts come to the host once and every chosen expert runs this
-package's products over its rows.  Either way a token's result does not depend on
-the other tokens of the step beyond the rounding of the products.
+package's products over its rows.  Either way a token's result does not depend on the other tokens of the step
+beyond the rounding of the products.
 NikolayBlagoev/garlic-inference's mixture-of-experts model is a different design (src/models/qwen3/qwen3-moe.cpp).
 """
 from __future__ import annotations
